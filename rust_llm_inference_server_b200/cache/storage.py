@@ -4,8 +4,8 @@ the same needs, and slots of fixed-size per-request state.
 Role of `PagedKvCache` (crates/model/src/paged.rs:23-152): there every layer has a K and a V
 tensor (slot, kv head, d) and a page id addresses the same rows in all of them.  Here the cache
 slots of the model's run order are sorted into groups by what they keep (head geometry, all
-tokens or a window); a group has one pool of pages, [slot in group, K|V, page, kv head, position
-in page, d], so one (page, head) tile is contiguous, and one block table per request.
+tokens or a window, keys and values or one row a token); a group has one pool of pages, [slot in
+group, K|V, page, kv head, position in page, d], so one (page, head) tile is contiguous, and one block table per request.
 """
 
 from __future__ import annotations
@@ -28,8 +28,13 @@ class CacheGroup:
     def window(self) -> int:
         return int(self.spec.window) if self.spec.window else 0
 
+    @property
+    def planes(self) -> int:
+        """2: keys and values; 1: a single row per token."""
+        return 2 if getattr(self.spec, "values", True) else 1
+
     def bytes_per_page(self, elem_size: int) -> int:
-        return len(self.slots) * 2 * self.spec.n_kv_heads * self.page_size * self.spec.head_dim * elem_size
+        return len(self.slots) * self.planes * self.spec.n_kv_heads * self.page_size * self.spec.head_dim * elem_size
 
 
 def plan_groups(slot_specs, page_size: int) -> list[CacheGroup]:
@@ -87,7 +92,7 @@ class CacheStorage:
             s = g.spec
             # Zeroed once and never cleared when pages are given back: correctness rests on
             # context lengths and masks, never on page contents (crates/model/src/paged.rs:53-60).
-            pool = torch.zeros((len(g.slots), 2, g.num_pages, s.n_kv_heads, g.page_size, s.head_dim),
+            pool = torch.zeros((len(g.slots), g.planes, g.num_pages, s.n_kv_heads, g.page_size, s.head_dim),
                                dtype=dtype, device=device)
             self.pools.append(pool)
             for i, slot in enumerate(g.slots):
@@ -104,7 +109,8 @@ class CacheStorage:
         if slot not in self._slot_home:
             return None
         gi, i = self._slot_home[slot]
-        return LayerCache(self.pools[gi][i, 0], self.pools[gi][i, 1], gi, self.groups[gi].page_size)
+        pool = self.pools[gi]
+        return LayerCache(pool[i, 0], pool[i, 1] if pool.shape[1] > 1 else None, gi, self.groups[gi].page_size)
 
     def bytes(self) -> int:
         return sum(p.numel() * p.element_size() for p in self.pools)

@@ -49,7 +49,13 @@ def registered_architectures() -> list[str]:
 def architecture_name(config_json: dict) -> str:
     archs = config_json.get("architectures")
     if archs is None:
-        return DEFAULT_ARCHITECTURE
+        # some designs name themselves with a single string under "architecture"
+        one = config_json.get("architecture")
+        if one is None:
+            return DEFAULT_ARCHITECTURE
+        if not isinstance(one, str) or not one:
+            raise ConfigError(f"config.json: 'architecture' must be a name, got {one!r}")
+        return one
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
         raise ConfigError(f"config.json: 'architectures' must be a list of names, got {archs!r}")
     return archs[0]

@@ -9,8 +9,13 @@ constexpr int BM = 64, BN = 64, BK = 16;
 
 __global__ __launch_bounds__(256) void sgemm_nt_kernel(const float* __restrict__ A,
                                                        const float* __restrict__ W,
-                                                       float* __restrict__ C, int M, int N, int K) {
+                                                       float* __restrict__ C, int M, int N, int K,
+                                                       long long lda, long long ldw, long long ldc,
+                                                       long long sa, long long sw, long long sc) {
     pdl_wait();
+    A += blockIdx.z * sa;      // one product a batch entry (blockIdx.z), each with the same sizes
+    W += blockIdx.z * sw;
+    C += blockIdx.z * sc;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -25,8 +30,8 @@ __global__ __launch_bounds__(256) void sgemm_nt_kernel(const float* __restrict__
         for (int i = threadIdx.x; i < BM * BK; i += 256) {
             const int r = i / BK, c = i % BK;
             const int gm = m0 + r, gn = n0 + r, gk = k0 + c;
-            As[c][r] = (gm < M && gk < K) ? A[(size_t)gm * K + gk] : 0.f;
-            Ws[c][r] = (gn < N && gk < K) ? W[(size_t)gn * K + gk] : 0.f;
+            As[c][r] = (gm < M && gk < K) ? A[(size_t)gm * lda + gk] : 0.f;
+            Ws[c][r] = (gn < N && gk < K) ? W[(size_t)gn * ldw + gk] : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -50,7 +55,7 @@ __global__ __launch_bounds__(256) void sgemm_nt_kernel(const float* __restrict__
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tx * 4 + j;
-            if (gn < N) C[(size_t)gm * N + gn] = acc[i][j];
+            if (gn < N) C[(size_t)gm * ldc + gn] = acc[i][j];
         }
     }
     pdl_trigger();   // the next kernel of the stream may start its launch
@@ -62,6 +67,19 @@ extern "C" int rlis_gemm_f32_nt(const float* A, const float* W, float* C, int M,
     if (M <= 0 || N <= 0) return 0;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return RLIS_ERR_UNSUPPORTED;
-    rlis_launch(sgemm_nt_kernel, grid, 256, 0, stream, A, W, C, M, N, K);
+    rlis_launch(sgemm_nt_kernel, grid, 256, 0, stream, A, W, C, M, N, K, (long long)K, (long long)K, (long long)N,
+                0LL, 0LL, 0LL);
+    return RLIS_LAUNCH_CHECK();
+}
+
+// `batch` products of the same sizes: entry b reads A + b * sa (rows lda apart), W + b * sw (rows ldw
+// apart) and writes C + b * sc (rows ldc apart); strides in elements.  The per-head maps of a mixer.
+extern "C" int rlis_gemm_f32_nt_batched(const float* A, const float* W, float* C, int M, int N, int K,
+                                        long long lda, long long ldw, long long ldc, int batch, long long sa,
+                                        long long sw, long long sc, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+    if (grid.y > 65535 || grid.z > 65535) return RLIS_ERR_UNSUPPORTED;
+    rlis_launch(sgemm_nt_kernel, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc, sa, sw, sc);
     return RLIS_LAUNCH_CHECK();
 }

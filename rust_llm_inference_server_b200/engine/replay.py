@@ -26,12 +26,13 @@ from ..models import load_model
 from .runner import ModelRunner, StepEntry
 
 REPLAY_PAGE_SIZE = 16
-MAX_LIVE_REQUESTS = 64
+# State slots (and so live requests) of a replay: few, so that slots are used again as requests end.
+MAX_LIVE_REQUESTS = 4
 
 
 class ReplaySession:
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = REPLAY_PAGE_SIZE,
-                 device: str = "cuda"):
+                 device: str = "cuda", max_live: int = MAX_LIVE_REQUESTS):
         if not torch.cuda.is_available():
             raise RuntimeError("trace replay needs a CUDA device; there is no CPU path")
         self.model = load_model(model_dir, dtype, device)
@@ -42,8 +43,9 @@ class ReplaySession:
         n_pages = max(1, (int(max_tokens) + page_size - 1) // page_size)
         for g in groups:
             g.num_pages = n_pages
-        self.cache = make_cache_manager(groups, MAX_LIVE_REQUESTS)
-        self.storage = CacheStorage(groups, self.model.call_state_specs, MAX_LIVE_REQUESTS,
+        self.max_live = int(max_live)
+        self.cache = make_cache_manager(groups, self.max_live)
+        self.storage = CacheStorage(groups, self.model.call_state_specs, self.max_live,
                                     self.model.dtype, self.model.device)
         self.runner = ModelRunner(self.model, self.cache, self.storage,
                                   max_seq_len=n_pages * page_size)
@@ -67,7 +69,7 @@ class ReplaySession:
             toks = [int(t) for t in e["tokens"]]
             start = self._count[sid]
             if self.cache.acquire_state_slot(sid) < 0:
-                raise RuntimeError(f"more than {MAX_LIVE_REQUESTS} live requests")
+                raise RuntimeError(f"more than {self.max_live} live requests")
             if not self.cache.reserve(sid, start + len(toks)):
                 raise RuntimeError(f"request {e['id']}: out of cache pages at {start + len(toks)} tokens "
                                    f"(the pool was made for --max-tokens)")
@@ -92,10 +94,10 @@ class ReplaySession:
 
 
 def run_replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, stream=None,
-               page_size: int = REPLAY_PAGE_SIZE) -> int:
+               page_size: int = REPLAY_PAGE_SIZE, max_live: int = MAX_LIVE_REQUESTS) -> int:
     stream = stream if stream is not None else sys.stdin
     os.makedirs(out_dir, exist_ok=True)
-    session = ReplaySession(model_dir, dtype, max_tokens, page_size)
+    session = ReplaySession(model_dir, dtype, max_tokens, page_size, max_live=max_live)
     for line in stream:
         line = line.strip()
         if not line:

@@ -183,6 +183,185 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
     return out
 
 
+def gemm_f32_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[:, b, :] = a[:, b, :] @ w[b]^T for every b, in true float32 (the same kernel and k order as
+    `gemm_f32`).  a [M, B, K], out [M, B, N]: views whose last axis has unit stride (the per-head
+    slices of wider rows); w [B, N, K] contiguous."""
+    M, B, K = a.shape
+    N = w.shape[1]
+    for t, nm in ((a, "a"), (out, "out")):
+        if t.dtype != torch.float32 or not t.is_cuda or t.stride(2) != 1:
+            raise KernelError(f"gemm_f32_batched: {nm} must be float32 on the device with unit stride in its last axis")
+    _req(w, "w", torch.float32, (B, N, K))
+    if tuple(out.shape) != (M, B, N):
+        raise KernelError(f"gemm_f32_batched: expected out of shape {(M, B, N)}, got {tuple(out.shape)}")
+    check(lib().rlis_gemm_f32_nt_batched(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), K,
+                                         out.stride(0), B, a.stride(1), N * K, out.stride(1), _stream()),
+          "gemm_f32_batched")
+    _count("gemm_f32.batched")
+    return out
+
+
+def per_head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, h, :] = w[h] @ a[t, h, :]: one small product a head (a [T, H, K] and out [T, H, N] may be
+    slices of wider rows, w [H, N, K]).  float32: this package's FFMA kernel; bfloat16 operands: the
+    library's batched GEMM with float32 accumulation, into `out`'s element type."""
+    if a.dtype == torch.float32:
+        return gemm_f32_batched(a, w, out)
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not a.is_cuda:
+        raise KernelError(f"per_head_linear: expected float32 or bfloat16 operands on the device, got {a.dtype}, {w.dtype}")
+    res = torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out_dtype=out.dtype) if out.dtype != a.dtype \
+        else torch.bmm(a.transpose(0, 1), w.transpose(1, 2))
+    out.copy_(res.transpose(0, 1))
+    return out
+
+
+def post_norm_residual(sub: torch.Tensor, resid: torch.Tensor, w_post: torch.Tensor, eps_post: float,
+                       scale: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+                       w_next: torch.Tensor | None = None, eps_next: float = 0.0,
+                       out: torch.Tensor | None = None):
+    """resid += scale * rmsnorm(sub + bias) * w_post, all in float32 and in place; with `w_next` also
+    out = rmsnorm(resid) * w_next (the norm in front of the next sublayer), rounded once to sub's type.
+    sub [T, H] in the activation type; resid float32 [T, H]; the vectors float32 [H]."""
+    T, H = resid.shape
+    _req(resid, "resid", torch.float32)
+    _req(sub, "sub", None, (T, H))
+    _req(w_post, "w_post", torch.float32, (H,))
+    for v, nm in ((scale, "scale"), (bias, "bias"), (w_next, "w_next")):
+        if v is not None:
+            _req(v, nm, torch.float32, (H,))
+    if w_next is not None:
+        _req(out, "out", sub.dtype, (T, H))
+    check(lib().rlis_post_norm_residual(sub.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                        w_post.data_ptr(), scale.data_ptr() if scale is not None else None,
+                                        resid.data_ptr(), w_next.data_ptr() if w_next is not None else None,
+                                        out.data_ptr() if w_next is not None else None, T, H, float(eps_post),
+                                        float(eps_next), _code(sub.dtype), _stream()), "post_norm_residual")
+    _count("post_norm_residual" + (".next" if w_next is not None else ""))
+    return out if w_next is not None else None
+
+
+def act_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+             gate: torch.Tensor | None = None) -> torch.Tensor:
+    """out = x / sqrt(mean(x^2) + eps) * weight (* sigmoid(gate)) per row, statistics in float32.  x is
+    float32 or out's type; x, gate and out [T, W] may be column slices of wider rows (unit stride in
+    the last axis)."""
+    T, W = x.shape
+    for t, nm in ((x, "x"), (out, "out")) + (((gate, "gate"),) if gate is not None else ()):
+        if not t.is_cuda or t.dim() != 2 or tuple(t.shape) != (T, W) or t.stride(1) != 1:
+            raise KernelError(f"act_norm: {nm} must be [T, W] rows on the device with unit stride")
+    if x.dtype not in (torch.float32, out.dtype) or (gate is not None and gate.dtype != out.dtype):
+        raise KernelError(f"act_norm: element types {x.dtype} / {out.dtype} are not taken")
+    _req(weight, "weight", torch.float32, (W,))
+    check(lib().rlis_act_norm(x.data_ptr(), x.stride(0), 1 if x.dtype == torch.float32 else 0, weight.data_ptr(),
+                              gate.data_ptr() if gate is not None else None,
+                              gate.stride(0) if gate is not None else 0, out.data_ptr(), out.stride(0), T, W,
+                              float(eps), _code(out.dtype), _stream()), "act_norm")
+    _count("act_norm" + (".gate" if gate is not None else ""))
+    return out
+
+
+BIAS_ACTIVATIONS = {"none": 0, "relu2": 1}
+
+
+def bias_act(x: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, activation: str = "none") -> torch.Tensor:
+    """out = act(x + bias): "none", or "relu2" (the square of max(., 0)); float32 inside."""
+    T, W = x.shape
+    _req(x, "x")
+    _req(out, "out", x.dtype, (T, W))
+    if bias is not None:
+        _req(bias, "bias", torch.float32, (W,))
+    if activation not in BIAS_ACTIVATIONS:
+        raise KernelError(f"bias_act: unknown activation {activation!r}; known: {sorted(BIAS_ACTIVATIONS)}")
+    check(lib().rlis_bias_act(x.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(), T, W,
+                              BIAS_ACTIVATIONS[activation], _code(x.dtype), _stream()), "bias_act")
+    _count("bias_act." + activation)
+    return out
+
+
+def latent_kv_store(z: torch.Tensor, weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, rot_dims: int,
+                    magnitude: float, positions: torch.Tensor, slots: torch.Tensor, cache: torch.Tensor,
+                    rank: int, page_size: int) -> None:
+    """Writes one row per token into a paged cache of latents [pages, 1, page_size, rank + rot]:
+    rmsnorm(z[:, :rank]) * weight, then z[:, rank:] with its first `rot_dims` entries rotated
+    (rotate-half, angle position * inv_freq, cos and sin times `magnitude`).  z may be a column slice."""
+    T, Wd = z.shape
+    rot = Wd - rank
+    if not z.is_cuda or z.stride(1) != 1 or rot < 0:
+        raise KernelError("latent_kv_store: z must be [T, rank + rot] rows on the device with unit stride")
+    _req(weight, "weight", torch.float32, (rank,))
+    _req(inv_freq, "inv_freq", torch.float32, (rot_dims // 2,))
+    _req(positions, "positions", torch.int32, (T,))
+    _req(slots, "slots", torch.int32, (T,))
+    _req(cache, "cache", z.dtype, (None, 1, page_size, Wd))
+    check(lib().rlis_latent_kv_store(z.data_ptr(), z.stride(0), weight.data_ptr(), inv_freq.data_ptr(),
+                                     positions.data_ptr(), slots.data_ptr(), cache.data_ptr(), T, rank, rot,
+                                     int(rot_dims), float(magnitude), float(eps), _code(z.dtype), _stream()),
+          "latent_kv_store")
+    _count("latent_kv_store")
+
+
+def latent_q_rope(q: torch.Tensor, qa: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int, magnitude: float,
+                  positions: torch.Tensor, n_heads: int, d_plain: int, rot: int, rank: int) -> torch.Tensor:
+    """qa[t, h, rank:] = the rotated part q[t, h, d_plain:] after rotation, in float32.  q [T, nh (d_plain
+    + rot)] in the activation type; qa float32 [T, nh (rank + rot)]."""
+    T = q.shape[0]
+    _req(q, "q", None, (T, n_heads * (d_plain + rot)))
+    _req(qa, "qa", torch.float32, (T, n_heads * (rank + rot)))
+    _req(inv_freq, "inv_freq", torch.float32, (rot_dims // 2,))
+    _req(positions, "positions", torch.int32, (T,))
+    check(lib().rlis_latent_q_rope(q.data_ptr(), qa.data_ptr(), inv_freq.data_ptr(), positions.data_ptr(), T,
+                                   n_heads, d_plain, rot, int(rot_dims), rank, float(magnitude), _code(q.dtype),
+                                   _stream()), "latent_q_rope")
+    _count("latent_q_rope")
+    return qa
+
+
+def attention_latent(qa: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, step, group: int, n_heads: int,
+                     rank: int, page_size: int, scale: float, sinks: torch.Tensor | None = None,
+                     window: int = 0) -> torch.Tensor:
+    """Causal attention of every token of the step over its request's cached latent rows, which all
+    heads share: score = scale * qa[t, h] . row, out[t, h] = sum of softmax weights times row[:rank].
+    `sinks` float32 [nh]: exp(sink_h) joins the denominator of head h and nothing else.  qa float32
+    [T, nh dk]; cache [pages, 1, page_size, dk]; out [T, nh rank] in the cache's type."""
+    T = qa.shape[0]
+    dk = cache.shape[-1]
+    _req(qa, "qa", torch.float32, (T, n_heads * dk))
+    _req(cache, "cache", None, (None, 1, page_size, dk))
+    _req(out, "out", cache.dtype, (T, n_heads * rank))
+    if sinks is not None:
+        _req(sinks, "sinks", torch.float32, (n_heads,))
+    tables = step.block_tables[group]
+    check(lib().rlis_attention_latent(qa.data_ptr(), cache.data_ptr(), out.data_ptr(),
+                                      sinks.data_ptr() if sinks is not None else None,
+                                      step.seq_of_token.data_ptr(), step.positions.data_ptr(), tables.data_ptr(),
+                                      None, tables.shape[1], T, n_heads, dk, rank, page_size, float(scale),
+                                      int(window), _code(cache.dtype), _stream()), "attention_latent")
+    _count("attention_latent")
+    return out
+
+
+def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torch.Tensor, state: torch.Tensor,
+                   decay: torch.Tensor, step, n_heads: int, d: int, dv: int) -> torch.Tensor:
+    """The decayed linear-attention recurrence over the step's tokens: per request and head
+    S <- decay_h S + k v^T, o = S^T q, with q, k, v = silu of columns q_off.., k_off.., v_off.. of
+    `proj` [T, *].  `state` float32 [slots, nh, d, dv] holds S between steps (a request whose first
+    token is in this step starts from zero); out float32 [T, nh dv]."""
+    T = proj.shape[0]
+    _req(proj, "proj")
+    _req(out, "out", torch.float32, (T, n_heads * dv))
+    _req(state, "state", torch.float32, (None, n_heads, d, dv))
+    _req(decay, "decay", torch.float32, (n_heads,))
+    if max(q_off, k_off) + n_heads * d > proj.shape[1] or v_off + n_heads * dv > proj.shape[1]:
+        raise KernelError("lightning_scan: the column offsets reach beyond the projection's rows")
+    check(lib().rlis_lightning_scan(proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, out.data_ptr(),
+                                    state.data_ptr(), decay.data_ptr(), step.cu_seqlens.data_ptr(),
+                                    step.ctx_lens.data_ptr(), step.state_slots.data_ptr(), step.n_seqs, n_heads, d,
+                                    dv, _code(proj.dtype), _stream()), "lightning_scan")
+    _count("lightning_scan")
+    return out
+
+
 FUSE_NORMS = True          # debug switch "fuse_norms": 0 runs every norm as a kernel
 STREAM_MAX_ROWS = 128     # what the weight-streaming kernel takes
 DECODE_GEMM_ROWS = 16     # up to this many rows its sink epilogue works: the norms go into the products

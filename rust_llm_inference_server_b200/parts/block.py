@@ -14,7 +14,7 @@ blocks: the model names the next block, and `entry_sink` answers for its first n
 from __future__ import annotations
 
 from .. import ops
-from .base import (build_feed_forward, build_mixer, build_norm, register_arrangement)
+from .base import (Part, build_feed_forward, build_mixer, build_norm, register_arrangement)
 
 
 class PreNormBlock:
@@ -49,4 +49,89 @@ class PreNormBlock:
         return resid, self.feed_forward.forward(h, step)
 
 
+class SandwichBlock:
+    """x += scale1 * post_norm1(mixer(norm1(x))); x += scale2 * post_norm2(feed_forward(norm2(x))),
+    the second line only when the layer has a feed-forward.  The residual stream and both norms of
+    a sublayer's result are float32: one kernel norms the result, scales it, adds it to the stream
+    and norms the stream for the sublayer that follows, also when that is the first sublayer of the
+    next block of this kind (the block then returns those rows as `NormedRows`).  A block returns no
+    pending delta: its additions are done when it returns."""
+
+    def __init__(self, spec, dtype, device):
+        self.dtype = dtype
+        self.norm1 = build_norm(spec.norm1, dtype, device)
+        self.mixer = build_mixer(spec.mixer, dtype, device)
+        self.post_norm1 = build_norm(spec.post_norm1, dtype, device)
+        self.scale1_name, self.scale2_name = spec.scale1, spec.scale2
+        self.hidden = spec.norm1.dim
+        self.feed_forward = build_feed_forward(spec.feed_forward, dtype, device) if spec.feed_forward is not None else None
+        self.norm2 = build_norm(spec.norm2, dtype, device) if self.feed_forward is not None else None
+        self.post_norm2 = build_norm(spec.post_norm2, dtype, device) if self.feed_forward is not None else None
+        self.scale1 = self.scale2 = None
+        for n in (self.norm1, self.post_norm1, self.norm2, self.post_norm2):
+            if n is not None and not hasattr(n, "weight"):
+                raise ValueError("the sandwich arrangement takes norms that are a weight and an eps (RMSNorm)")
+
+    chains_norms = True      # `forward` takes `next_block`
+
+    def entry_sink(self, resid, step):
+        return None          # nothing is left to the product before this block
+
+    def parts(self):
+        own = _BlockTensors(self)
+        return tuple(p for p in (self.norm1, self.mixer, self.post_norm1, self.norm2, self.feed_forward,
+                                 self.post_norm2, own) if p is not None)
+
+    def _last(self, sub, resid, post_norm, scale, step, next_block, bias=None):
+        """The block's last addition; norms the stream for the next block when that is a sandwich too."""
+        if isinstance(next_block, SandwichBlock):
+            h = step.buffer("norm_out", (resid.shape[0], self.hidden), self.dtype)
+            ops.post_norm_residual(sub, resid, post_norm.weight, post_norm.eps, scale, bias=bias,
+                                   w_next=next_block.norm1.weight, eps_next=next_block.norm1.eps, out=h)
+            return resid, NormedRows(h)
+        ops.post_norm_residual(sub, resid, post_norm.weight, post_norm.eps, scale, bias=bias)
+        return resid, None
+
+    def forward(self, resid, pending, step, cache, state, writes_cache=True, next_block=None):
+        h = pending.x if isinstance(pending, NormedRows) else self.norm1.forward(resid, pending, step)
+        a = self.mixer.forward(h, step, cache, state, writes_cache)
+        if self.feed_forward is None:
+            return self._last(a, resid, self.post_norm1, self.scale1, step, next_block)
+        h = step.buffer("norm_out", (resid.shape[0], self.hidden), self.dtype)
+        ops.post_norm_residual(a, resid, self.post_norm1.weight, self.post_norm1.eps, self.scale1,
+                               w_next=self.norm2.weight, eps_next=self.norm2.eps, out=h)
+        defer = getattr(self.feed_forward, "b_down", None) is not None
+        f = self.feed_forward.forward(h, step, defer_bias=True) if defer else self.feed_forward.forward(h, step)
+        return self._last(f, resid, self.post_norm2, self.scale2, step, next_block,
+                          bias=self.feed_forward.b_down if defer else None)
+
+
+class NormedRows:
+    """What a block hands the next one when it has already normed the stream for it: `x`, the next
+    block's first norm applied to the (complete) residual stream."""
+
+    def __init__(self, x):
+        self.x = x
+
+
+class _BlockTensors(Part):
+    """The block's own tensors (the per-channel scales), loaded with its parts."""
+
+    graph_safe = True
+
+    def __init__(self, block):
+        self.block = block
+
+    def tensors(self) -> dict:
+        b = self.block
+        return {n: (b.hidden,) for n in (b.scale1_name, b.scale2_name if b.feed_forward is not None else None)
+                if n is not None}
+
+    def load(self, src) -> None:
+        b = self.block
+        b.scale1 = src.get(b.scale1_name, "vector") if b.scale1_name is not None else None
+        b.scale2 = src.get(b.scale2_name, "vector") if (b.scale2_name is not None and b.feed_forward is not None) else None
+
+
 register_arrangement("prenorm", PreNormBlock)
+register_arrangement("sandwich", SandwichBlock)

@@ -58,4 +58,47 @@ class SwiGLU(FeedForward):
             return ops.linear(act, self.w_down, sink=sink)
 
 
+class DenseFF(FeedForward):
+    """W_down act(W_up x + b_up) + b_down.  The bias and the activation after the first product are
+    one kernel; the second bias is returned as `pending_bias` for an arrangement that norms the
+    result (it adds the bias while it reads the row), and added here otherwise."""
+
+    graph_safe = True
+
+    def __init__(self, spec, dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        if spec.activation not in ops.BIAS_ACTIVATIONS:
+            raise ValueError(f"unknown activation {spec.activation!r}; known: {sorted(ops.BIAS_ACTIVATIONS)}")
+
+    def tensors(self) -> dict:
+        s = self.spec
+        out = {s.up_proj: (s.intermediate, s.hidden), s.down_proj: (s.hidden, s.intermediate)}
+        if s.up_bias is not None:
+            out[s.up_bias] = (s.intermediate,)
+        if s.down_bias is not None:
+            out[s.down_bias] = (s.hidden,)
+        return out
+
+    def load(self, src) -> None:
+        s = self.spec
+        self.w_up = src.get(s.up_proj).contiguous()
+        self.w_down = src.get(s.down_proj).contiguous()
+        self.b_up = src.get(s.up_bias, "vector") if s.up_bias is not None else None
+        self.b_down = src.get(s.down_bias, "vector") if s.down_bias is not None else None
+
+    def forward(self, x, step, defer_bias: bool = False):
+        """With `defer_bias` the caller adds `self.b_down` itself (in float32, while norming)."""
+        with span("mlp up proj"):
+            u = ops.linear(x, self.w_up)
+        with span("bias + activation"):
+            act = ops.bias_act(u, self.b_up, step.buffer("ffn_act", tuple(u.shape), self.dtype), self.spec.activation)
+        with span("mlp down proj"):
+            y = ops.linear(act, self.w_down)
+        if self.b_down is not None and not defer_bias:
+            y = ops.bias_act(y, self.b_down, step.buffer("ffn_out", tuple(y.shape), self.dtype), "none")
+        return y
+
+
 register_feed_forward("swiglu", SwiGLU)
+register_feed_forward("dense_ff", DenseFF)

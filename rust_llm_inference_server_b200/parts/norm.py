@@ -12,7 +12,8 @@ from .base import Norm, register_norm
 
 class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * w.  eps is used as a float32 (layers.rs:115); the sum of
-    squares and the scale are float32; the weight is held in float32 (an exact widening)."""
+    squares and the scale are float32; the weight is held in float32 (an exact widening).  A spec
+    with an `offset` (a weight stored around zero) has it added once at load time, in float32."""
 
     graph_safe = True    # launches depend on the step's device arrays and shapes only
 
@@ -20,6 +21,7 @@ class RMSNorm(Norm):
         self.dim = spec.dim
         self.eps = float(np.float32(spec.eps))
         self.weight_name = spec.weight
+        self.offset = float(getattr(spec, "offset", 0.0))
         self.dtype = dtype
         self.weight = None
 
@@ -28,6 +30,8 @@ class RMSNorm(Norm):
 
     def load(self, src) -> None:
         self.weight = src.get(self.weight_name, "vector")
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()
 
     def forward(self, resid, delta, step):
         out = step.buffer("norm_out", (resid.shape[0], self.dim), self.dtype)

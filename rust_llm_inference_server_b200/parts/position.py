@@ -38,11 +38,34 @@ def rope_inverse_frequencies(head_dim: int, theta: float, scaling=None) -> np.nd
     return out.astype(np.float32)
 
 
+def yarn_inverse_frequencies(dims: int, base: float, factor=None, original: float = 0.0, fast: float = 0.0,
+                             slow: float = 0.0):
+    """(float32 [dims / 2] frequencies, multiplier of cos and sin) of `YarnRopeSpec`'s rule, worked out
+    in float64 and rounded once."""
+    half = dims // 2
+    i = np.arange(half, dtype=np.float64)
+    f = np.power(float(base), -2.0 * i / dims)
+    if factor is None:
+        return f.astype(np.float32), 1.0
+
+    def dim_of(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(dim_of(fast)), 0)
+    hi = min(math.ceil(dim_of(slow)), dims - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    f = f / factor * ramp + f * (1.0 - ramp)
+    return f.astype(np.float32), 0.1 * math.log(factor) + 1.0
+
+
 class Rope(PositionEncoding):
     def __init__(self, spec, dtype, device):
         self.head_dim = spec.head_dim
         inv = rope_inverse_frequencies(spec.head_dim, spec.theta, spec.scaling)
         self.inv_freq = torch.from_numpy(inv).to(device)
+
+    def rotation(self):
+        return self.inv_freq, self.head_dim, 1.0
 
     def encode_and_store(self, qkv, q_out, cache, step, n_heads, n_kv_heads, head_dim, store):
         slots = step.slots[cache.group] if (store and cache is not None) else None
@@ -72,5 +95,22 @@ class NoPosition(PositionEncoding):
         return None
 
 
+class YarnRope(PositionEncoding):
+    """A rotation a mixer applies itself: `rotation()` gives (float32 frequencies on the device, how
+    many leading entries are rotated, the multiplier of cos and sin)."""
+
+    def __init__(self, spec, dtype, device):
+        if spec.dims <= 0 or spec.dims % 2:
+            raise ValueError(f"a rotate-half rotation takes an even number of entries, got {spec.dims}")
+        inv, self.magnitude = yarn_inverse_frequencies(spec.dims, spec.base, spec.factor, spec.original,
+                                                       spec.fast, spec.slow)
+        self.dims = int(spec.dims)
+        self.inv_freq = torch.from_numpy(inv).to(device)
+
+    def rotation(self):
+        return self.inv_freq, self.dims, float(self.magnitude)
+
+
 register_position("rope", Rope)
+register_position("yarn_rope", YarnRope)
 register_position("none", NoPosition)

@@ -16,9 +16,11 @@ from typing import Any, Optional
 
 @dataclass(frozen=True)
 class RMSNormSpec:
+    """y = x / sqrt(mean(x^2) + eps) * (offset + w).  `offset` 1 is a weight stored around zero."""
     dim: int
     eps: float
     weight: str                      # tensor name, shape (dim,)
+    offset: float = 0.0
     kind: str = "rmsnorm"
 
 
@@ -29,6 +31,23 @@ class RopeSpec:
     theta: float
     scaling: Any = None
     kind: str = "rope"
+
+
+@dataclass(frozen=True)
+class YarnRopeSpec:
+    """Rotate-half rotary encoding over the first `dims` entries of a vector (the rest pass
+    unchanged) with YaRN's frequency blend: with dim(t) = dims ln(original / (2 pi t)) / (2 ln base),
+    lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims - 1) and ramp_i = clamp((i - lo) /
+    max(hi - lo, 0.001), 0, 1), frequency i is f_i / factor * ramp_i + f_i (1 - ramp_i), f_i =
+    base^(-2i / dims), and cos and sin are multiplied by 0.1 ln(factor) + 1.  `factor` None: the plain
+    frequencies f_i and no multiplier."""
+    dims: int
+    base: float
+    factor: Optional[float] = None
+    original: float = 0.0
+    fast: float = 0.0
+    slow: float = 0.0
+    kind: str = "yarn_rope"
 
 
 @dataclass(frozen=True)
@@ -53,6 +72,71 @@ class GQAAttentionSpec:
     window: Optional[int] = None
     scale: Optional[float] = None
     kind: str = "gqa_attention"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are linear maps of a cached latent.  Per token the
+    cache holds [c | k_rot]: c = rmsnorm(W_dkv h)[:kv_rank] * kv_norm and the rotated key part
+    (`rot_dim` wide, shared by all heads).  Queries: q = W_uq (rmsnorm(W_dq h) * q_norm), per head
+    [dim unrotated | rot_dim rotated].  Head h: key = [W_uk_h c | k_rot], value = W_uv_h c, score =
+    scale * q . key.  `sink`: a tensor (n_heads,) whose exp joins each head's softmax denominator.
+    `kv_down` None: the layer has no W_dkv and reads the cache slot of another call."""
+    hidden: int
+    n_heads: int
+    dim: int                         # unrotated query/key entries per head
+    rot_dim: int                     # rotated entries per head
+    v_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    eps: float
+    q_down: str                      # (q_rank, hidden)
+    q_norm: str                      # (q_rank,)
+    q_up: str                        # (n_heads * (dim + rot_dim), q_rank)
+    kv_down: Optional[str]           # (kv_rank + rot_dim, hidden)
+    kv_norm: Optional[str]           # (kv_rank,)
+    k_up: str                        # (n_heads * dim, kv_rank)
+    v_up: str                        # (n_heads * v_dim, kv_rank)
+    o_proj: str                      # (hidden, n_heads * v_dim)
+    sink: Optional[str] = None       # (n_heads,)
+    position: Any = field(default_factory=NoPositionSpec)
+    window: Optional[int] = None
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class LightningAttentionSpec:
+    """Linear attention with a per-head decay: q, k = silu(W h) (n_heads x dim), v = silu(W_v h)
+    (n_heads x v_dim); S_t = decay_h S_(t-1) + k_t v_t^T (float32 state per request), o_t = S_t^T q_t;
+    out = W_o (rmsnorm(o) * out_norm * sigmoid(W_g h))."""
+    hidden: int
+    n_heads: int
+    dim: int
+    v_dim: int
+    decay: tuple                     # one factor per head
+    eps: float
+    q_proj: str                      # (n_heads * dim, hidden)
+    k_proj: str
+    v_proj: str                      # (n_heads * v_dim, hidden)
+    gate_proj: str                   # (n_heads * v_dim, hidden)
+    out_norm: str                    # (n_heads * v_dim,)
+    o_proj: str                      # (hidden, n_heads * v_dim)
+    kind: str = "lightning_attention"
+
+
+@dataclass(frozen=True)
+class DenseFFSpec:
+    """W_down act(W_up h + b_up) + b_down; `activation` "relu2" is the square of max(., 0).  The
+    biases are optional tensors."""
+    hidden: int
+    intermediate: int
+    up_proj: str                     # (intermediate, hidden)
+    down_proj: str                   # (hidden, intermediate)
+    up_bias: Optional[str] = None    # (intermediate,)
+    down_bias: Optional[str] = None  # (hidden,)
+    activation: str = "relu2"
+    kind: str = "dense_ff"
 
 
 @dataclass(frozen=True)
@@ -92,12 +176,19 @@ class LMHeadSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One block.  arrangement "prenorm": x += mixer(norm1(x)); x += feed_forward(norm2(x))
-    (crates/model/src/llama.rs:264-271)."""
+    (crates/model/src/llama.rs:264-271).  arrangement "sandwich": each sublayer's result is normed
+    and scaled before it joins the stream, x += scale1 * post_norm1(mixer(norm1(x))) and the same
+    with norm2, feed_forward, post_norm2, scale2; `feed_forward` None leaves the second sublayer out
+    (norm2, post_norm2 and scale2 are then None too)."""
     norm1: Any
     mixer: Any
     norm2: Any
     feed_forward: Any
     arrangement: str = "prenorm"
+    post_norm1: Any = None
+    post_norm2: Any = None
+    scale1: Optional[str] = None     # tensor name, shape (hidden,): per-channel scale of the sublayer's result
+    scale2: Optional[str] = None
 
 
 @dataclass(frozen=True)

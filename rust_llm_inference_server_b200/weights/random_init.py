@@ -20,6 +20,8 @@ from ..config.registry import lookup_architecture
 from .safetensors_io import save_file
 
 _STORE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+# kinds other than "matrix" and "norm": "offset" (weights stored around zero, biases), "gain" (free scalars)
+_STD = {"offset": 0.1, "gain": 1.0}
 
 
 def _tensor_key(seed: int, name: str) -> list[int]:
@@ -29,7 +31,7 @@ def _tensor_key(seed: int, name: str) -> list[int]:
 
 def random_tensor(seed: int, name: str, shape, kind: str, std: float = 0.02) -> torch.Tensor:
     rng = np.random.Generator(np.random.Philox(key=_tensor_key(seed, name)))
-    x = rng.standard_normal(size=tuple(shape), dtype=np.float32) * np.float32(std)
+    x = rng.standard_normal(size=tuple(shape), dtype=np.float32) * np.float32(_STD.get(kind, std))
     if kind == "norm":
         x += np.float32(1.0)
     return torch.from_numpy(x)
@@ -54,7 +56,7 @@ def random_tensors_on_device(config_json: dict, seed: int, device, store_dtype: 
     gen.manual_seed(int(seed))
     out = {}
     for name, (shape, kind) in kinds.items():
-        x = torch.randn(tuple(shape), generator=gen, device=device, dtype=torch.float32) * 0.02
+        x = torch.randn(tuple(shape), generator=gen, device=device, dtype=torch.float32) * _STD.get(kind, 0.02)
         if kind == "norm":
             x += 1.0
         out[name] = x.to(_STORE[store_dtype])
@@ -68,7 +70,8 @@ def write_random_model(config_json: dict, out_dir: str, seed: int, store_dtype: 
     save_file(tensors, os.path.join(out_dir, "model.safetensors"),
               metadata={"format": "pt", "random_weights_seed": seed})
     cfg = dict(config_json)
-    cfg.setdefault("architectures", [lookup_architecture(config_json).name])
+    if "architecture" not in cfg:
+        cfg.setdefault("architectures", [lookup_architecture(config_json).name])
     cfg["torch_dtype"] = store_dtype
     with open(os.path.join(out_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(cfg, f, indent=2)
