@@ -419,6 +419,130 @@ def workload_1b_fp32(args, torch, np) -> dict:
     }
 
 
+def lasapel_config(width: int, vocab: int = 32000) -> dict:
+    """Four Lasapel layers at a real model's proportions: heads of 128, a latent of 512 with 64
+    rotated entries, a query latent of 3/4 of the width, feed-forwards of four widths."""
+    H = width // 128
+    rot = {"dims": 64, "base": 10000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    lat = {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 3 * width // 4, "kv_rank": 512,
+           "scale": (128 + 64) ** -0.5, "rot": rot}
+    lin = {"heads": H, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, H - 1)) for h in range(H)]}
+    mlp = {"kind": "dense", "ff": 4 * width}
+    return {"architecture": "Lasapel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": [
+        {"type": "lightning", "mixer": lin, "mlp": mlp}, {"type": "latent_attention", "mixer": lat, "mlp": mlp},
+        {"type": "lightning", "mixer": lin, "mlp": None}, {"type": "latent_attention", "mixer": dict(lat, kv_from=1), "mlp": mlp}]}
+
+
+def llama_config_like(width: int, vocab: int = 32000) -> dict:
+    """The closest existing model at the same width and depth: heads of 64, four query heads a key
+    head, a gated feed-forward of the same parameter count as the dense one of four widths (8/3)."""
+    return {"architectures": ["LlamaForCausalLM"], "hidden_size": width, "intermediate_size": width * 8 // 3 // 128 * 128,
+            "num_hidden_layers": 4, "num_attention_heads": width // 64, "num_key_value_heads": width // 256,
+            "head_dim": 64, "vocab_size": vocab, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+            "max_position_embeddings": 131072, "tie_word_embeddings": False}
+
+
+def prefill_run(llm, tokens: int, iters: int, warmup: int, torch, np) -> float:
+    """Median device time (ms) of one prompt of `tokens` tokens run whole, logits at its last place."""
+    from rust_llm_inference_server_b200.engine import StepEntry
+    rng = np.random.default_rng(1)
+    V, cache, runner = llm.model.spec.vocab_size, llm.engine.cache, llm.engine.runner
+    times = []
+    for it in range(warmup + iters):
+        sid = 700 + it
+        cache.acquire_state_slot(sid)
+        assert cache.reserve(sid, tokens)
+        toks = rng.integers(0, V, size=tokens).tolist()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        runner.step([StepEntry(sid, toks, 0, [tokens - 1])])
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+        cache.free(sid)
+    return statistics.median(times[warmup:])
+
+
+def workload_lasapel(args, torch, np) -> dict:
+    """Prefill (one 2,048-token prompt) and decode (batch 8, context 4,096) of four Lasapel layers
+    at two widths beside four Llama layers of the same width, random bfloat16 weights; then the
+    stages of one step by CUDA-event spans, with the mixers' kernels against their rooflines."""
+    from rust_llm_inference_server_b200 import LLM
+    from rust_llm_inference_server_b200.ops import profile
+    pk, pk_src = peaks()
+    B, ctx, page, T = args.batch, args.context, 16, PREFILL_TOKENS
+    steps = min(args.steps, 64)
+    out = {"workload": "lasapel", "metric": "prefill and decode tokens/s of four layers, Lasapel beside Llama at equal width",
+           "unit": "tokens/s", "impl": "ours", "dtype": "bf16", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+           "data": "synthetic: uniform-random token ids, random-init weights (device generator)",
+           "config": {"global_batch": B, "seq_len": ctx, "prefill_tokens": T, "page_size": page, "layers": 4},
+           "peaks": dict(pk, source=pk_src), "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for width in (1024, 2048):
+        row = {}
+        for name, cfg in (("lasapel", lasapel_config(width)), ("llama", llama_config_like(width))):
+            llm = LLM.from_random(cfg, 8, dtype="bfloat16", on_device=True, max_seq_len=ctx + page,
+                                  num_blocks=B * (ctx + page) // page + 64, block_size=page, max_num_seqs=B,
+                                  max_batched_tokens=max(2048, B), prefix_caching=False)
+            pre = prefill_run(llm, T, 5, 3, torch, np)
+            ms, launches = decode_run(llm, B, steps, args.warmup, ctx, torch)
+            profile.enable(True)                      # the same two steps by stages (eager, events around each)
+            prefill_run(llm, T, 3, 2, torch, np)
+            profile.take_report()
+            prefill_run(llm, T, 3, 0, torch, np)
+            pre_stages = {k: round(v[0] / 3 * 1e3, 1) for k, v in profile.take_report().items()}
+            decode_run(llm, B, 8, 4, ctx, torch, fill=False)
+            dec_stages = {k: round(v[0] / 8 * 1e3, 1) for k, v in profile.take_report().items()}
+            profile.enable(False)
+            row[name] = {"prefill_tokens_per_s": round(T / (pre / 1e3), 1), "prefill_ms": round(pre, 3),
+                         "decode_tokens_per_s": round(B / (ms / 1e3), 1), "decode_ms_per_step": round(ms, 4),
+                         "launches_per_decode_step": launches,
+                         "weight_bytes": int(sum(p.numel() * p.element_size() for p in _model_tensors(llm.model))),
+                         "prefill_stage_us": pre_stages, "decode_stage_us": dec_stages}
+            del llm
+            torch.cuda.empty_cache()
+        H = width // 128
+        la, ll = row["lasapel"], row["llama"]
+        hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+        mean_ctx = ctx - 4
+
+        def frac(ideal_s, stage_us, calls):
+            return round(ideal_s / (stage_us / calls * 1e-6), 4) if stage_us else None
+
+        # per launch: latent attention reads one row of 576 a key for all heads; grouped-query attention a key and a
+        # value of 64 for every key head; the recurrence reads and writes its float32 state
+        row["rooflines"] = {
+            "latent_attention_decode": frac(max(B * mean_ctx * 576 * 2 / hbm, 2 * B * H * mean_ctx * (576 + 512) / tf),
+                                            la["decode_stage_us"].get("attention"), 2),
+            "gqa_attention_decode": frac(B * mean_ctx * (width // 256) * 64 * 2 * 2 / hbm,
+                                         ll["decode_stage_us"].get("rope + kv write + attention"), 4),
+            "latent_attention_prefill": frac(2 * H * (576 + 512) * T * (T + 1) / 2 / tf, la["prefill_stage_us"].get("attention"), 2),
+            "gqa_attention_prefill": frac(2 * (width // 64) * (64 + 64) * T * (T + 1) / 2 / tf,
+                                          ll["prefill_stage_us"].get("attention"), 4),
+            "recurrence_decode": frac(B * H * 128 * 128 * 4 * 2 / hbm, la["decode_stage_us"].get("decayed recurrence"), 2),
+            "recurrence_prefill_fp32_flops": frac(4 * T * H * 128 * 128 / (pk.get("fp32_tflops", 75.0) * 1e12),
+                                                  la["prefill_stage_us"].get("decayed recurrence"), 2),
+        }
+        out["sizes"][f"width{width}"] = row
+    out["clocks"] = clocks.stop()
+    head = out["sizes"]["width2048"]["lasapel"]
+    out["value"] = head["decode_tokens_per_s"]
+    out["ms_per_step"] = head["decode_ms_per_step"]
+    out["gpu_launches"] = int(round(head["launches_per_decode_step"] * steps))
+    return out
+
+
+def _model_tensors(model):
+    seen = {}
+    for part in model.parts():
+        for v in vars(part).values():
+            if isinstance(v, type(model.embedding.weight)) and v.is_cuda:
+                seen[v.data_ptr()] = v
+    return seen.values()
+
+
 def print_timeline(records: list) -> None:
     """One decode step product by product (microseconds since the first product of the step started):
     when the launch's first CTA started, when its wait for the kernel before it passed, when its
@@ -439,7 +563,7 @@ def print_timeline(records: list) -> None:
         prev = r["end"]
 
 
-WORKLOADS = {"3b": workload_3b, "8b": workload_8b, "1b-fp32": workload_1b_fp32}
+WORKLOADS = {"3b": workload_3b, "8b": workload_8b, "1b-fp32": workload_1b_fp32, "lasapel": workload_lasapel}
 
 
 def main() -> int:

@@ -26,8 +26,9 @@ from ..models import load_model
 from .runner import ModelRunner, StepEntry
 
 REPLAY_PAGE_SIZE = 16
-# State slots (and so live requests) of a replay: few, so that slots are used again as requests end.
-MAX_LIVE_REQUESTS = 4
+# State slots (and so live requests) of a session unless the caller says otherwise; `bin/trace_run`
+# asks for few, so that slots are used again as requests end.
+MAX_LIVE_REQUESTS = 64
 
 
 class ReplaySession:
