@@ -1,0 +1,444 @@
+// Attention over a cache of latent rows on the tensor cores (bfloat16; mma.sync m16n8k16 with
+// float32 sums), for prompt portions and for single decoded tokens.  The contract is that of
+// attention_latent.cu: a row [latent | rotated key part] of DK entries a token, shared by all heads;
+// score = scale * qa . row; values are the first DV entries of the same rows; an optional sink term
+// exp(sink_h) in a head's softmax denominator.
+//
+// A CTA of 8 warps works on 64-key stages brought to shared memory by 16-byte asynchronous copies,
+// double-buffered, rows padded by 8 entries.  A warp holds 16 query rows and HALF of the value
+// columns (DV / 2: its output sums are DV / 4 registers a thread), so two warps share their rows
+// and both form the scores.
+//   prompts: one head x 64 tokens a CTA; warp pair p takes tokens 16 p .. 16 p + 15 and every key.
+//   decode : 16 heads of one token a CTA, and one piece of its context; warp pair p takes keys
+//            16 p .. 16 p + 15 of every stage, and the four pairs' running (max, sum, output) are
+//            merged through shared memory at the end.  Several pieces of a context are merged by
+//            a second small kernel.
+// Queries arrive as float32 and are rounded to bfloat16 once, into shared memory.
+#include "common.cuh"
+#include "mma_utils.cuh"
+#include <math.h>
+
+namespace {
+constexpr int LF_THREADS = 256;
+constexpr int LF_BN = 64;                 // keys a stage
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct LatentArgs {
+    const float* qa;          // [T, nh, dk]
+    const bf16* cache;        // [pages, 1, page, dk]
+    bf16* out;                // [T, nh, dv]
+    const float* sinks;       // [nh] or null
+    const int* tiles;         // prompts: [n][2] (batch entry, first token of the tile)
+    const int* cu_seqlens;
+    const int* ctx_lens;
+    const int* block_tables;
+    const int* dec_rows;      // decode: token row and batch entry of every single token
+    const int* dec_seqs;
+    float* scratch;           // decode, several pieces: [n_dec][head tiles][pieces][16][dv + 2]
+    int max_blocks, nh, dk, page_size, window, pieces, piece_keys;
+    float scale;
+};
+
+// PREFILL: 64 query rows a CTA, every warp pair sees all 64 keys of a stage (8 score tiles).
+// decode : 16 query rows a CTA, warp pair p sees keys 16 p .. 16 p + 15 of a stage (2 score tiles).
+template <int DV, bool PREFILL>
+__global__ __launch_bounds__(LF_THREADS) void latent_flash_kernel(const LatentArgs a) {
+    pdl_wait();
+    constexpr int NT = PREFILL ? 8 : 2;          // score tiles (8 keys each) a warp forms a stage
+    constexpr int QR = PREFILL ? 64 : 16;        // query rows a CTA
+    constexpr int NO = DV / 16;                  // output tiles (8 columns each) a warp owns: half of DV / 8
+    const int dk = a.dk, stride = dk + 8, ksteps = dk / 16, cpr = dk / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);              // [QR][stride]
+    bf16* kbuf = qs + QR * stride;                             // [2][64][stride]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, c = lane & 3;
+    const int half = warp & 1, pair = warp >> 1;
+    const int nh = a.nh;
+
+    int b, q_row0, n_q_rows, head0, pos_base, k_lo, k_hi;
+    if (PREFILL) {
+        b = a.tiles[2 * blockIdx.y];
+        const int t0 = a.tiles[2 * blockIdx.y + 1];
+        const int q_start = a.cu_seqlens[b], q_len = a.cu_seqlens[b + 1] - q_start;
+        q_row0 = q_start + t0;
+        n_q_rows = min(64, q_len - t0);
+        head0 = blockIdx.x;
+        pos_base = a.ctx_lens[b] - q_len + t0;                 // position of the tile's first token
+        k_hi = pos_base + n_q_rows;                            // exclusive
+        k_lo = a.window > 0 ? max(0, pos_base - a.window + 1) : 0;
+    } else {
+        const int di = blockIdx.y;
+        b = a.dec_seqs[di];
+        q_row0 = a.dec_rows[di];
+        n_q_rows = 1;
+        head0 = blockIdx.x * 16;
+        pos_base = a.ctx_lens[b] - 1;
+        const int lo = a.window > 0 ? max(0, pos_base - a.window + 1) : 0;
+        k_lo = max(lo, blockIdx.z * a.piece_keys);
+        k_hi = min(pos_base + 1, (int)(blockIdx.z + 1) * a.piece_keys);
+    }
+    const int* table = a.block_tables + (size_t)b * a.max_blocks;
+
+    // queries -> shared memory, rounded to bfloat16; rows beyond the tile (or the heads) are zero
+    for (int idx = threadIdx.x; idx < QR * (dk / 2); idx += LF_THREADS) {
+        const int r = idx / (dk / 2), j = (idx - r * (dk / 2)) * 2;
+        float2 v = make_float2(0.f, 0.f);
+        if (PREFILL) {
+            if (r < n_q_rows) v = *reinterpret_cast<const float2*>(a.qa + ((size_t)(q_row0 + r) * nh + head0) * dk + j);
+        } else {
+            if (head0 + r < nh) v = *reinterpret_cast<const float2*>(a.qa + ((size_t)q_row0 * nh + head0 + r) * dk + j);
+        }
+        *reinterpret_cast<uint32_t*>(qs + r * stride + j) = pack_bf16(v.x, v.y);
+    }
+
+    const int kt0 = k_lo / LF_BN, kt1 = k_hi > k_lo ? (k_hi + LF_BN - 1) / LF_BN : kt0;
+    const int page_size = a.page_size;
+    // four threads copy a key's row, 16 bytes each in turn; a thread looks its key's page up once a stage
+    const int key_in = threadIdx.x >> 2, sub = threadIdx.x & 3;
+    auto issue = [&](int kt, int stage) {
+        const int key = kt * LF_BN + key_in;
+        const bool valid = key < k_hi && key >= k_lo;
+        const bf16* src = a.cache;
+        if (valid) {
+            const int pi = key / page_size;
+            src += ((size_t)table[pi] * page_size + (key - pi * page_size)) * dk;
+        }
+        bf16* dst = kbuf + ((size_t)stage * LF_BN + key_in) * stride;
+        for (int c16 = sub; c16 < cpr; c16 += 4) cp_async16(dst + c16 * 8, src + c16 * 8, valid);
+        cp_async_commit();
+    };
+
+    // this lane's two rows (g and g + 8 of the warp's 16)
+    const int row_base = PREFILL ? pair * 16 : 0;
+    int pos0, pos1, h0, h1;
+    bool rv0, rv1;
+    if (PREFILL) {
+        rv0 = row_base + g < n_q_rows;
+        rv1 = row_base + g + 8 < n_q_rows;
+        pos0 = pos_base + row_base + g;
+        pos1 = pos0 + 8;
+        h0 = h1 = head0;
+    } else {
+        h0 = head0 + g;
+        h1 = h0 + 8;
+        rv0 = h0 < nh;
+        rv1 = h1 < nh;
+        pos0 = pos1 = pos_base;
+    }
+    const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+    const int lo1 = a.window > 0 ? max(0, pos1 - a.window + 1) : 0;
+    // the sink is one more key, with a score of its own and no value; in decode it belongs to the first
+    // piece's first warp pair
+    const bool has_sink = a.sinks != nullptr && (PREFILL || (blockIdx.z == 0 && pair == 0));
+    float m_run[2], l_run[2];
+    m_run[0] = has_sink && rv0 ? a.sinks[h0] * LOG2E : -INFINITY;
+    m_run[1] = has_sink && rv1 ? a.sinks[h1] * LOG2E : -INFINITY;
+    l_run[0] = has_sink && rv0 ? 1.f : 0.f;
+    l_run[1] = has_sink && rv1 ? 1.f : 0.f;
+    float oacc[NO][4];
+#pragma unroll
+    for (int n = 0; n < NO; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[n][e] = 0.f;
+    const float scale_log2 = a.scale * LOG2E;
+    const int key_off = PREFILL ? 0 : pair * 16;             // this warp's keys within a stage
+    const int col0 = half * (DV / 2);                        // this warp's value columns
+
+    int stage = 0;
+    if (kt0 < kt1) issue(kt0, 0);
+    for (int kt = kt0; kt < kt1; ++kt) {
+        if (kt + 1 < kt1) {
+            issue(kt + 1, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const bf16* ks_ = kbuf + (size_t)stage * LF_BN * stride + (size_t)key_off * stride;
+
+        float sacc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sacc[nt][e] = 0.f;
+        for (int ks = 0; ks < ksteps; ++ks) {
+            uint32_t qa[4];
+            ldmatrix_x4(qa, qs + (row_base + ((lane >> 3) & 1) * 8 + (lane & 7)) * stride + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nt2 = 0; nt2 < NT / 2; ++nt2) {
+                uint32_t kb[4];
+                ldmatrix_x4(kb, ks_ + ((nt2 * 2 + (lane >> 4)) * 8 + (lane & 7)) * stride + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16_16816(sacc[2 * nt2], qa, kb[0], kb[1]);
+                mma_bf16_16816(sacc[2 * nt2 + 1], qa, kb[2], kb[3]);
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+        const int key_base = kt * LF_BN + key_off;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key_base + nt * 8 + 2 * c + e;
+                float s0 = sacc[nt][e] * scale_log2, s1 = sacc[nt][2 + e] * scale_log2;
+                if (!(rv0 && key <= pos0 && key >= lo0 && key >= k_lo && key < k_hi)) s0 = -INFINITY;
+                if (!(rv1 && key <= pos1 && key >= lo1 && key >= k_lo && key < k_hi)) s1 = -INFINITY;
+                sacc[nt][e] = s0;
+                sacc[nt][2 + e] = s1;
+                mx0 = fmaxf(mx0, s0);
+                mx1 = fmaxf(mx1, s1);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float corr0 = exp2f(m_run[0] - ms0), corr1 = exp2f(m_run[1] - ms1);
+        float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float p0 = exp2f(sacc[nt][e] - ms0), p1 = exp2f(sacc[nt][2 + e] - ms1);
+                sacc[nt][e] = p0;
+                sacc[nt][2 + e] = p1;
+                ls0 += p0;
+                ls1 += p1;
+            }
+        ls0 += __shfl_xor_sync(0xffffffffu, ls0, 1);
+        ls0 += __shfl_xor_sync(0xffffffffu, ls0, 2);
+        ls1 += __shfl_xor_sync(0xffffffffu, ls1, 1);
+        ls1 += __shfl_xor_sync(0xffffffffu, ls1, 2);
+        l_run[0] = l_run[0] * corr0 + ls0;
+        l_run[1] = l_run[1] * corr1 + ls1;
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+#pragma unroll
+        for (int n = 0; n < NO; ++n) {
+            oacc[n][0] *= corr0;
+            oacc[n][1] *= corr0;
+            oacc[n][2] *= corr1;
+            oacc[n][3] *= corr1;
+        }
+#pragma unroll
+        for (int kk = 0; kk < NT / 2; ++kk) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(sacc[2 * kk][0], sacc[2 * kk][1]);
+            pa[1] = pack_bf16(sacc[2 * kk][2], sacc[2 * kk][3]);
+            pa[2] = pack_bf16(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
+            pa[3] = pack_bf16(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < NO / 2; ++n2) {
+                uint32_t vb[4];
+                const int mat = lane >> 3;
+                ldmatrix_x4_trans(vb, ks_ + (kk * 16 + (mat & 1) * 8 + (lane & 7)) * stride + col0 + (n2 * 2 + (mat >> 1)) * 8);
+                mma_bf16_16816(oacc[2 * n2], pa, vb[0], vb[1]);
+                mma_bf16_16816(oacc[2 * n2 + 1], pa, vb[2], vb[3]);
+            }
+        }
+        __syncthreads();
+        stage ^= 1;
+    }
+
+    if (PREFILL) {
+        const float inv0 = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f;
+        const float inv1 = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
+        if (rv0) {
+            bf16* o = a.out + ((size_t)(q_row0 + row_base + g) * nh + head0) * DV + col0;
+#pragma unroll
+            for (int n = 0; n < NO; ++n)
+                *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(oacc[n][0] * inv0, oacc[n][1] * inv0);
+        }
+        if (rv1) {
+            bf16* o = a.out + ((size_t)(q_row0 + row_base + g + 8) * nh + head0) * DV + col0;
+#pragma unroll
+            for (int n = 0; n < NO; ++n)
+                *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(oacc[n][2] * inv1, oacc[n][3] * inv1);
+        }
+        pdl_trigger();
+        return;
+    }
+
+    // decode: merge the four warp pairs (their keys differ) through shared memory, which the key
+    // stages no longer need: ml [4 pairs][16 rows][2], then sums [16][DV] float32
+    float* ml = reinterpret_cast<float*>(kbuf);
+    float* osum = ml + 4 * 16 * 2;
+    if (half == 0 && c == 0) {
+        ml[(pair * 16 + g) * 2] = m_run[0];
+        ml[(pair * 16 + g) * 2 + 1] = l_run[0];
+        ml[(pair * 16 + g + 8) * 2] = m_run[1];
+        ml[(pair * 16 + g + 8) * 2 + 1] = l_run[1];
+    }
+    __syncthreads();
+    float mg0 = -INFINITY, mg1 = -INFINITY;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        mg0 = fmaxf(mg0, ml[(p * 16 + g) * 2]);
+        mg1 = fmaxf(mg1, ml[(p * 16 + g + 8) * 2]);
+    }
+    const float ms0 = mg0 == -INFINITY ? 0.f : mg0, ms1 = mg1 == -INFINITY ? 0.f : mg1;
+    float lg0 = 0.f, lg1 = 0.f;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        lg0 += ml[(p * 16 + g) * 2 + 1] * exp2f(ml[(p * 16 + g) * 2] - ms0);
+        lg1 += ml[(p * 16 + g + 8) * 2 + 1] * exp2f(ml[(p * 16 + g + 8) * 2] - ms1);
+    }
+    const float w0 = exp2f(m_run[0] - ms0), w1 = exp2f(m_run[1] - ms1);
+    for (int p = 0; p < 4; ++p) {
+        if (pair == p) {
+#pragma unroll
+            for (int n = 0; n < NO; ++n) {
+                float* r0 = osum + g * DV + col0 + n * 8 + 2 * c;
+                float* r1 = osum + (g + 8) * DV + col0 + n * 8 + 2 * c;
+                if (p == 0) {
+                    r0[0] = oacc[n][0] * w0; r0[1] = oacc[n][1] * w0;
+                    r1[0] = oacc[n][2] * w1; r1[1] = oacc[n][3] * w1;
+                } else {
+                    r0[0] += oacc[n][0] * w0; r0[1] += oacc[n][1] * w0;
+                    r1[0] += oacc[n][2] * w1; r1[1] += oacc[n][3] * w1;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    // rows (heads) x DV sums are complete; every thread takes a share of the columns
+    if (a.pieces == 1) {
+        if (pair == 0) {       // the two warps of pair 0 hold (mg, lg) of rows g and g + 8 in their lanes
+            const float inv0 = lg0 > 0.f ? 1.0f / lg0 : 0.f, inv1 = lg1 > 0.f ? 1.0f / lg1 : 0.f;
+            if (rv0) {
+                bf16* o = a.out + ((size_t)q_row0 * nh + h0) * DV + col0;
+                const float* r = osum + g * DV + col0;
+#pragma unroll
+                for (int n = 0; n < NO; ++n)
+                    *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(r[n * 8 + 2 * c] * inv0, r[n * 8 + 2 * c + 1] * inv0);
+            }
+            if (rv1) {
+                bf16* o = a.out + ((size_t)q_row0 * nh + h1) * DV + col0;
+                const float* r = osum + (g + 8) * DV + col0;
+#pragma unroll
+                for (int n = 0; n < NO; ++n)
+                    *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(r[n * 8 + 2 * c] * inv1, r[n * 8 + 2 * c + 1] * inv1);
+            }
+        }
+    } else {
+        float* part = a.scratch + (((size_t)blockIdx.y * gridDim.x + blockIdx.x) * a.pieces + blockIdx.z) * 16 * (DV + 2);
+        if (pair == 0) {
+            float* p0 = part + g * (DV + 2);
+            float* p1 = part + (g + 8) * (DV + 2);
+            if (half == 0 && c == 0) {
+                p0[DV] = mg0; p0[DV + 1] = lg0;
+                p1[DV] = mg1; p1[DV + 1] = lg1;
+            }
+#pragma unroll
+            for (int n = 0; n < NO; ++n) {
+                const int col = col0 + n * 8 + 2 * c;
+                p0[col] = osum[g * DV + col]; p0[col + 1] = osum[g * DV + col + 1];
+                p1[col] = osum[(g + 8) * DV + col]; p1[col + 1] = osum[(g + 8) * DV + col + 1];
+            }
+        }
+    }
+    pdl_trigger();
+}
+
+// One CTA a (decoded token, head): folds the pieces' (max, sum, output) into the output row.
+template <int DV>
+__global__ void latent_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out,
+                                    const int* __restrict__ dec_rows, int nh, int head_tiles, int pieces) {
+    pdl_wait_and_trigger();
+    const int di = blockIdx.y, h = blockIdx.x;
+    const float* part = scratch + (((size_t)di * head_tiles + h / 16) * pieces) * 16 * (DV + 2) + (size_t)(h % 16) * (DV + 2);
+    const size_t piece_stride = (size_t)16 * (DV + 2);
+    float m = -INFINITY;
+    for (int p = 0; p < pieces; ++p) m = fmaxf(m, part[p * piece_stride + DV]);
+    const float ms = m == -INFINITY ? 0.f : m;
+    float l = 0.f;
+    for (int p = 0; p < pieces; ++p) l += part[p * piece_stride + DV + 1] * exp2f(part[p * piece_stride + DV] - ms);
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    bf16* o = out + ((size_t)dec_rows[di] * nh + h) * DV;
+    for (int col = threadIdx.x; col < DV; col += blockDim.x) {
+        float acc = 0.f;
+        for (int p = 0; p < pieces; ++p) acc += part[p * piece_stride + col] * exp2f(part[p * piece_stride + DV] - ms);
+        o[col] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <bool PREFILL> size_t latent_smem_bytes(int dk, int dv) {
+    const size_t stages = (size_t)((PREFILL ? 64 : 16) + 2 * LF_BN) * (dk + 8) * sizeof(bf16);
+    const size_t merge = PREFILL ? 0 : (size_t)16 * (dk + 8) * sizeof(bf16) + (4 * 16 * 2 + (size_t)16 * dv) * sizeof(float);
+    return stages > merge ? stages : merge;
+}
+
+template <int DV, bool PREFILL>
+int launch_latent(const LatentArgs& a, dim3 grid, int dv, cudaStream_t stream) {
+    const size_t smem = latent_smem_bytes<PREFILL>(a.dk, dv);
+    if (smem > 227 * 1024) return RLIS_ERR_UNSUPPORTED;
+    static size_t allowed = 0;
+    if (smem > allowed) {
+        cudaFuncSetAttribute(latent_flash_kernel<DV, PREFILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        allowed = smem;
+    }
+    rlis_launch(latent_flash_kernel<DV, PREFILL>, grid, LF_THREADS, smem, stream, a);
+    return RLIS_LAUNCH_CHECK();
+}
+}  // namespace
+
+// Whether the tensor-core kernels take these sizes: value widths of 64, 128, 256 or 512 and rows
+// that are multiples of 16 entries and fit shared memory with two stages of keys.
+extern "C" int rlis_attention_latent_mma_takes(int dk, int dv) {
+    if (!(dv == 64 || dv == 128 || dv == 256 || dv == 512) || dk % 16 || dk < dv || dk <= 0) return 0;
+    return latent_smem_bytes<true>(dk, dv) <= 227 * 1024 ? 1 : 0;
+}
+
+extern "C" int rlis_attention_latent_prefill(const float* qa, const void* cache, void* out, const float* sinks,
+                                             const int* tiles, int n_tiles, const int* cu_seqlens,
+                                             const int* ctx_lens, const int* block_tables, int max_blocks, int nh,
+                                             int dk, int dv, int page_size, float scale, int window,
+                                             cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (!rlis_attention_latent_mma_takes(dk, dv) || n_tiles > 65535 || nh <= 0) return RLIS_ERR_UNSUPPORTED;
+    LatentArgs a = {qa, (const bf16*)cache, (bf16*)out, sinks, tiles, cu_seqlens, ctx_lens, block_tables, nullptr,
+                    nullptr, nullptr, max_blocks, nh, dk, page_size, window, 1, 0, scale};
+    dim3 grid(nh, n_tiles);
+    switch (dv) {
+        case 64: return launch_latent<64, true>(a, grid, dv, stream);
+        case 128: return launch_latent<128, true>(a, grid, dv, stream);
+        case 256: return launch_latent<256, true>(a, grid, dv, stream);
+        default: return launch_latent<512, true>(a, grid, dv, stream);
+    }
+}
+
+// pieces > 1: `scratch` holds n_dec * ceil(nh / 16) * pieces * 16 * (dv + 2) floats and the context
+// is cut into pieces of `piece_keys` keys (a multiple of 64).
+extern "C" int rlis_attention_latent_decode(const float* qa, const void* cache, void* out, const float* sinks,
+                                            float* scratch, const int* dec_rows, const int* dec_seqs,
+                                            const int* ctx_lens, const int* block_tables, int max_blocks, int n_dec,
+                                            int nh, int dk, int dv, int page_size, float scale, int window,
+                                            int pieces, int piece_keys, cudaStream_t stream) {
+    if (n_dec <= 0) return 0;
+    if (!rlis_attention_latent_mma_takes(dk, dv) || n_dec > 65535 || nh <= 0 || pieces < 1 || pieces > 65535 ||
+        (pieces > 1 && (scratch == nullptr || piece_keys <= 0 || piece_keys % LF_BN)))
+        return RLIS_ERR_UNSUPPORTED;
+    if (pieces == 1) piece_keys = 0x40000000;
+    LatentArgs a = {qa, (const bf16*)cache, (bf16*)out, sinks, nullptr, nullptr, ctx_lens, block_tables, dec_rows,
+                    dec_seqs, scratch, max_blocks, nh, dk, page_size, window, pieces, piece_keys, scale};
+    const int head_tiles = (nh + 15) / 16;
+    dim3 grid(head_tiles, n_dec, pieces);
+    int rc;
+    switch (dv) {
+        case 64: rc = launch_latent<64, false>(a, grid, dv, stream); break;
+        case 128: rc = launch_latent<128, false>(a, grid, dv, stream); break;
+        case 256: rc = launch_latent<256, false>(a, grid, dv, stream); break;
+        default: rc = launch_latent<512, false>(a, grid, dv, stream); break;
+    }
+    if (rc != 0 || pieces == 1) return rc;
+    dim3 mgrid(nh, n_dec);
+    switch (dv) {
+        case 64: rlis_launch(latent_merge_kernel<64>, mgrid, 64, 0, stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
+        case 128: rlis_launch(latent_merge_kernel<128>, mgrid, 128, 0, stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
+        case 256: rlis_launch(latent_merge_kernel<256>, mgrid, 128, 0, stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
+        default: rlis_launch(latent_merge_kernel<512>, mgrid, 128, 0, stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
+    }
+    return RLIS_LAUNCH_CHECK();
+}

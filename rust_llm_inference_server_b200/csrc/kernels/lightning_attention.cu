@@ -5,28 +5,36 @@
 //
 // The state of a request lives in its state slot between steps; a request whose first token is in
 // this step starts from zero.  Columns of S evolve independently, so a CTA takes (request, head,
-// 16 columns): 8 threads share a column, each holding d/8 of its entries in registers, and walk the
-// request's tokens of this step in order.  Tokens are staged through shared memory 16 at a time.
+// 32 columns): 8 threads share a column, each holding a contiguous eighth of its entries in
+// registers, and walk the request's tokens of this step in order.  Tokens are staged through shared
+// memory 16 at a time (silu applied once on the way in), the next 16 already on their way from
+// global memory while the current ones are worked on.
 // Everything after the projection is float32; the order of every sum depends on d only.
 #include "common.cuh"
 #include <math.h>
 
 namespace {
-constexpr int COLS = 16, SLICES = 8, TOK = 16, MAX_E = 32;   // d up to 256
+constexpr int COLS = 32, SLICES = 8, TOK = 16, MAX_E = 32;   // d up to 256
+constexpr int THREADS = COLS * SLICES;
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
-template <typename T>
-__global__ __launch_bounds__(COLS * SLICES) void lightning_scan_kernel(
+// E = entries of a column that one thread holds: ceil(d / 8), rounded up to a multiple of 4 so that a
+// thread reads its share of k and q from shared memory in 16-byte vectors.  Thread `slice` owns the
+// entries slice * E .. slice * E + E - 1 (those at or beyond d stay zero).
+template <typename T, int E>
+__global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
     const T* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, float* __restrict__ out,
     float* __restrict__ state, const float* __restrict__ decay, const int* __restrict__ cu_seqlens,
     const int* __restrict__ ctx_lens, const int* __restrict__ state_slots, int nh, int d, int dv) {
     pdl_wait_and_trigger();
-    extern __shared__ float sm[];
-    float* qs = sm;                       // [TOK][d]
-    float* ks = qs + TOK * d;             // [TOK][d]
-    float* vs = ks + TOK * d;             // [TOK][COLS]
-    float* os = vs + TOK * COLS;          // [TOK][COLS]
+    constexpr int DP = SLICES * E;                 // padded d
+    constexpr int ES = E + 4;                      // a thread's share sits 4 floats apart from the next one's: no bank conflicts
+    constexpr int DPS = SLICES * ES;
+    __shared__ __align__(16) float qs[TOK * DPS];
+    __shared__ __align__(16) float ks[TOK * DPS];
+    __shared__ float vs[TOK * COLS];
+    __shared__ float os[TOK * COLS];
     const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * COLS;
     const int row0 = cu_seqlens[b], n = cu_seqlens[b + 1] - row0;
     const int slice = threadIdx.x % SLICES, col = threadIdx.x / SLICES;
@@ -35,57 +43,101 @@ __global__ __launch_bounds__(COLS * SLICES) void lightning_scan_kernel(
     const int slot = state_slots[b];
     float* S = state + ((size_t)slot * nh + h) * d * dv;
     const float g = decay[h];
-    float s[MAX_E];
+    float s[E];
 #pragma unroll
-    for (int e = 0; e < MAX_E; ++e) {
-        const int i = slice + SLICES * e;
+    for (int e = 0; e < E; ++e) {
+        const int i = slice * E + e;
         s[e] = (!fresh && live && i < d) ? S[(size_t)i * dv + c0 + col] : 0.f;
     }
+    // what one thread stages of q and k: element idx = threadIdx.x + j * THREADS of the [TOK][DP] tile
+    constexpr int PER = TOK * DP / THREADS;
+    float rq[PER], rk[PER], rv[(TOK * COLS + THREADS - 1) / THREADS];
+    auto fetch = [&](int t0) {                     // raw values of the next tokens, into registers
+        const int nt = min(TOK, n - t0);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int idx = threadIdx.x + j * THREADS, tt = idx / DP, i = idx - tt * DP;
+            const bool ok = tt < nt && i < d;
+            const T* r = proj + (size_t)(row0 + t0 + (ok ? tt : 0)) * stride + h * d + (ok ? i : 0);
+            rq[j] = ok ? to_f<T>(r[q_off]) : 0.f;
+            rk[j] = ok ? to_f<T>(r[k_off]) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < (TOK * COLS + THREADS - 1) / THREADS; ++j) {
+            const int idx = threadIdx.x + j * THREADS, tt = idx / COLS, c = idx - tt * COLS;
+            const bool ok = idx < TOK * COLS && tt < nt && c0 + c < dv;
+            rv[j] = ok ? to_f<T>(proj[(size_t)(row0 + t0 + tt) * stride + v_off + h * dv + c0 + c]) : 0.f;
+        }
+    };
+    if (n > 0) fetch(0);
     for (int t0 = 0; t0 < n; t0 += TOK) {
         const int nt = min(TOK, n - t0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * d; idx += blockDim.x) {
-            const int tt = idx / d, i = idx - tt * d;
-            const T* r = proj + (size_t)(row0 + t0 + tt) * stride + h * d + i;
-            qs[tt * d + i] = silu_f(to_f<T>(r[q_off]));
-            ks[tt * d + i] = silu_f(to_f<T>(r[k_off]));
+        __syncthreads();                           // the last tile's readers are done
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int idx = threadIdx.x + j * THREADS, tt = idx / DP, i = idx - tt * DP;
+            const int at = tt * DPS + (i / E) * ES + i % E;
+            qs[at] = silu_f(rq[j]);                // silu(0) = 0 keeps the padding zero
+            ks[at] = silu_f(rk[j]);
         }
-        for (int idx = threadIdx.x; idx < nt * COLS; idx += blockDim.x) {
-            const int tt = idx / COLS, c = idx - tt * COLS;
-            vs[idx] = c0 + c < dv ? silu_f(to_f<T>(proj[(size_t)(row0 + t0 + tt) * stride + v_off + h * dv + c0 + c])) : 0.f;
+#pragma unroll
+        for (int j = 0; j < (TOK * COLS + THREADS - 1) / THREADS; ++j) {
+            const int idx = threadIdx.x + j * THREADS;
+            if (idx < TOK * COLS) vs[idx] = silu_f(rv[j]);
         }
         __syncthreads();
+        if (t0 + TOK < n) fetch(t0 + TOK);         // in flight while this tile is worked on
         for (int tt = 0; tt < nt; ++tt) {
             const float v = vs[tt * COLS + col];
-            const float* kr = ks + tt * d;
-            const float* qr = qs + tt * d;
-            float o = 0.f;
+            const float4* kr = reinterpret_cast<const float4*>(ks + tt * DPS + slice * ES);
+            const float4* qr = reinterpret_cast<const float4*>(qs + tt * DPS + slice * ES);
+            float o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int e = 0; e < MAX_E; ++e) {
-                const int i = slice + SLICES * e;
-                if (i < d) {
-                    s[e] = fmaf(g, s[e], kr[i] * v);
-                    o = fmaf(s[e], qr[i], o);
-                }
+            for (int e4 = 0; e4 < E / 4; ++e4) {
+                const float4 k4 = kr[e4], q4 = qr[e4];
+                s[4 * e4 + 0] = fmaf(g, s[4 * e4 + 0], k4.x * v);
+                s[4 * e4 + 1] = fmaf(g, s[4 * e4 + 1], k4.y * v);
+                s[4 * e4 + 2] = fmaf(g, s[4 * e4 + 2], k4.z * v);
+                s[4 * e4 + 3] = fmaf(g, s[4 * e4 + 3], k4.w * v);
+                o[0] = fmaf(s[4 * e4 + 0], q4.x, o[0]);
+                o[1] = fmaf(s[4 * e4 + 1], q4.y, o[1]);
+                o[2] = fmaf(s[4 * e4 + 2], q4.z, o[2]);
+                o[3] = fmaf(s[4 * e4 + 3], q4.w, o[3]);
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            if (slice == 0) os[tt * COLS + col] = o;
+            float ot = (o[0] + o[1]) + (o[2] + o[3]);
+            ot += __shfl_xor_sync(0xffffffffu, ot, 1);
+            ot += __shfl_xor_sync(0xffffffffu, ot, 2);
+            ot += __shfl_xor_sync(0xffffffffu, ot, 4);
+            if (slice == 0) os[tt * COLS + col] = ot;
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * COLS; idx += blockDim.x) {
+        for (int idx = threadIdx.x; idx < nt * COLS; idx += THREADS) {
             const int tt = idx / COLS, c = idx - tt * COLS;
             if (c0 + c < dv) out[(size_t)(row0 + t0 + tt) * nh * dv + h * dv + c0 + c] = os[idx];
         }
     }
     if (live) {
 #pragma unroll
-        for (int e = 0; e < MAX_E; ++e) {
-            const int i = slice + SLICES * e;
+        for (int e = 0; e < E; ++e) {
+            const int i = slice * E + e;
             if (i < d) S[(size_t)i * dv + c0 + col] = s[e];
         }
     }
+}
+
+template <typename T>
+int launch_scan(const T* proj, long long stride, int q_off, int k_off, int v_off, float* out, float* state,
+                const float* decay, const int* cu, const int* ctx, const int* slots, dim3 grid, int nh, int d, int dv,
+                cudaStream_t stream) {
+    const int e = (d + SLICES - 1) / SLICES;
+#define RLIS_SCAN(E) rlis_launch(lightning_scan_kernel<T, E>, grid, THREADS, 0, stream, proj, stride, q_off, k_off, \
+                                 v_off, out, state, decay, cu, ctx, slots, nh, d, dv)
+    if (e <= 4) RLIS_SCAN(4);
+    else if (e <= 8) RLIS_SCAN(8);
+    else if (e <= 16) RLIS_SCAN(16);
+    else RLIS_SCAN(32);
+#undef RLIS_SCAN
+    return RLIS_LAUNCH_CHECK();
 }
 }  // namespace
 
@@ -97,14 +149,11 @@ extern "C" int rlis_lightning_scan(const void* proj, long long stride, int q_off
     if (d <= 0 || d > SLICES * MAX_E || dv <= 0 || nh <= 0 || nh > 65535) return RLIS_ERR_UNSUPPORTED;
     dim3 grid(n_seqs, nh, (dv + COLS - 1) / COLS);
     if (grid.z > 65535) return RLIS_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(2 * TOK * d + 2 * TOK * COLS) * sizeof(float);
     if (dtype == RLIS_F32)
-        rlis_launch(lightning_scan_kernel<float>, grid, COLS * SLICES, smem, stream, (const float*)proj, stride, q_off,
-                    k_off, v_off, out, state, decay, cu_seqlens, ctx_lens, state_slots, nh, d, dv);
-    else if (dtype == RLIS_BF16)
-        rlis_launch(lightning_scan_kernel<bf16>, grid, COLS * SLICES, smem, stream, (const bf16*)proj, stride, q_off,
-                    k_off, v_off, out, state, decay, cu_seqlens, ctx_lens, state_slots, nh, d, dv);
-    else
-        return RLIS_ERR_UNSUPPORTED;
-    return RLIS_LAUNCH_CHECK();
+        return launch_scan((const float*)proj, stride, q_off, k_off, v_off, out, state, decay, cu_seqlens, ctx_lens,
+                           state_slots, grid, nh, d, dv, stream);
+    if (dtype == RLIS_BF16)
+        return launch_scan((const bf16*)proj, stride, q_off, k_off, v_off, out, state, decay, cu_seqlens, ctx_lens,
+                           state_slots, grid, nh, d, dv, stream);
+    return RLIS_ERR_UNSUPPORTED;
 }

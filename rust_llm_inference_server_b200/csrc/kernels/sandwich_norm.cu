@@ -93,6 +93,147 @@ __global__ __launch_bounds__(THREADS) void act_norm_kernel(
     }
 }
 
+// Four consecutive elements as floats (16 bytes of float32, 8 of bfloat16).
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Quad<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+// The same two kernels for widths that are multiples of 4 on aligned rows: NV vectors of four a thread.
+template <typename T, int NV>
+__global__ __launch_bounds__(THREADS) void post_norm_residual_vec_kernel(
+    const T* __restrict__ sub, const float* __restrict__ bias, const float* __restrict__ w_post,
+    const float* __restrict__ scale, float* __restrict__ resid, const float* __restrict__ w_next,
+    T* __restrict__ out, int hidden, float eps_post, float eps_next) {
+    pdl_wait_and_trigger();
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (threadIdx.x + i * THREADS) * 4;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < hidden) {
+            v[i] = Quad<T>::load(sub + base + c);
+            if (bias != nullptr) {
+                const float4 b = Quad<float>::load(bias + c);
+                v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
+            }
+            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float r1 = 1.0f / sqrtf(ss / (float)hidden + eps_post);
+    float ss2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (threadIdx.x + i * THREADS) * 4;
+        if (c < hidden) {
+            const float4 w = Quad<float>::load(w_post + c);
+            const float4 s = scale != nullptr ? Quad<float>::load(scale + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+            float4 x = Quad<float>::load(resid + base + c);
+            const float n0 = v[i].x * r1 * w.x, n1 = v[i].y * r1 * w.y, n2 = v[i].z * r1 * w.z, n3 = v[i].w * r1 * w.w;
+            x.x += scale != nullptr ? s.x * n0 : n0;
+            x.y += scale != nullptr ? s.y * n1 : n1;
+            x.z += scale != nullptr ? s.z * n2 : n2;
+            x.w += scale != nullptr ? s.w * n3 : n3;
+            Quad<float>::store(resid + base + c, x);
+            v[i] = x;
+            ss2 = fmaf(x.x, x.x, ss2); ss2 = fmaf(x.y, x.y, ss2); ss2 = fmaf(x.z, x.z, ss2); ss2 = fmaf(x.w, x.w, ss2);
+        }
+    }
+    if (w_next == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float r2 = 1.0f / sqrtf(ss2 / (float)hidden + eps_next);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (threadIdx.x + i * THREADS) * 4;
+        if (c < hidden) {
+            const float4 w = Quad<float>::load(w_next + c);
+            Quad<T>::store(out + base + c, make_float4(v[i].x * r2 * w.x, v[i].y * r2 * w.y, v[i].z * r2 * w.z, v[i].w * r2 * w.w));
+        }
+    }
+}
+
+template <typename TIn, typename T, int NV>
+__global__ __launch_bounds__(THREADS) void act_norm_vec_kernel(
+    const TIn* __restrict__ x, long long x_stride, const float* __restrict__ w,
+    const T* __restrict__ gate, long long gate_stride, T* __restrict__ out, long long out_stride,
+    int width, float eps) {
+    pdl_wait_and_trigger();
+    __shared__ float scratch[33];
+    const TIn* xr = x + (size_t)blockIdx.x * x_stride;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (threadIdx.x + i * THREADS) * 4;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < width) {
+            v[i] = Quad<TIn>::load(xr + c);
+            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)width + eps);
+    T* orow = out + (size_t)blockIdx.x * out_stride;
+    const T* grow = gate != nullptr ? gate + (size_t)blockIdx.x * gate_stride : nullptr;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (threadIdx.x + i * THREADS) * 4;
+        if (c < width) {
+            const float4 ww = Quad<float>::load(w + c);
+            float4 y = make_float4(v[i].x * r * ww.x, v[i].y * r * ww.y, v[i].z * r * ww.z, v[i].w * r * ww.w);
+            if (grow != nullptr) {
+                const float4 gt = Quad<T>::load(grow + c);
+                y.x *= 1.0f / (1.0f + expf(-gt.x)); y.y *= 1.0f / (1.0f + expf(-gt.y));
+                y.z *= 1.0f / (1.0f + expf(-gt.z)); y.w *= 1.0f / (1.0f + expf(-gt.w));
+            }
+            Quad<T>::store(orow + c, y);
+        }
+    }
+}
+
+template <typename T>
+__global__ void bias_act_vec_kernel(const T* __restrict__ x, const float* __restrict__ b, T* __restrict__ out,
+                                    long long n4, int width, int act) {
+    pdl_wait_and_trigger();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+        float4 v = Quad<T>::load(x + i * 4);
+        if (b != nullptr) {
+            const float4 bb = Quad<float>::load(b + (i * 4) % width);
+            v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
+        }
+        if (act == 1) {
+            v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
+            v.x *= v.x; v.y *= v.y; v.z *= v.z; v.w *= v.w;
+        }
+        Quad<T>::store(out + i * 4, v);
+    }
+}
+
+template <typename T>
+static bool aligned_for_quads(const void* p) { return ((uintptr_t)p) % (4 * sizeof(T)) == 0; }
+
 // out = act(x + b): act 0 none, 1 the square of max(., 0).  Element-wise, float32 inside.
 template <typename T>
 __global__ void bias_act_kernel(const T* __restrict__ x, const float* __restrict__ b, T* __restrict__ out,
@@ -114,6 +255,17 @@ extern "C" int rlis_post_norm_residual(const void* sub, const float* bias, const
                                        float eps_post, float eps_next, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hidden <= 0 || hidden > THREADS * MAX_PER_THREAD) return RLIS_ERR_UNSUPPORTED;
+    if (hidden % 4 == 0 && (dtype == RLIS_F32 || dtype == RLIS_BF16)) {
+        const int nv = (hidden / 4 + THREADS - 1) / THREADS;
+#define RLIS_PNR(T, NV) rlis_launch(post_norm_residual_vec_kernel<T, NV>, n_tokens, THREADS, 0, stream, (const T*)sub, bias, \
+                                    w_post, scale, resid, w_next, (T*)out, hidden, eps_post, eps_next)
+#define RLIS_PNR_T(T) do { if (nv <= 1) RLIS_PNR(T, 1); else if (nv <= 2) RLIS_PNR(T, 2); else if (nv <= 4) RLIS_PNR(T, 4); \
+                           else RLIS_PNR(T, 8); } while (0)
+        if (dtype == RLIS_F32) RLIS_PNR_T(float); else RLIS_PNR_T(bf16);
+#undef RLIS_PNR_T
+#undef RLIS_PNR
+        return RLIS_LAUNCH_CHECK();
+    }
     if (dtype == RLIS_F32)
         rlis_launch(post_norm_residual_kernel<float>, n_tokens, THREADS, 0, stream, (const float*)sub, bias, w_post,
                     scale, resid, w_next, (float*)out, hidden, eps_post, eps_next);
@@ -131,6 +283,24 @@ extern "C" int rlis_act_norm(const void* x, long long x_stride, int x_f32, const
                              float eps, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (width <= 0 || width > THREADS * MAX_PER_THREAD) return RLIS_ERR_UNSUPPORTED;
+    const bool in32 = dtype == RLIS_F32 || x_f32;
+    const bool quads = width % 4 == 0 && x_stride % 4 == 0 && gate_stride % 4 == 0 && out_stride % 4 == 0 &&
+                       (in32 ? aligned_for_quads<float>(x) : aligned_for_quads<bf16>(x)) &&
+                       (dtype == RLIS_F32 ? aligned_for_quads<float>(out) && aligned_for_quads<float>(gate)
+                                          : aligned_for_quads<bf16>(out) && aligned_for_quads<bf16>(gate));
+    if (quads && (dtype == RLIS_F32 || dtype == RLIS_BF16)) {
+        const int nv = (width / 4 + THREADS - 1) / THREADS;
+#define RLIS_AN(TI, T, NV) rlis_launch(act_norm_vec_kernel<TI, T, NV>, n_tokens, THREADS, 0, stream, (const TI*)x, x_stride, w, \
+                                       (const T*)gate, gate_stride, (T*)out, out_stride, width, eps)
+#define RLIS_AN_T(TI, T) do { if (nv <= 1) RLIS_AN(TI, T, 1); else if (nv <= 2) RLIS_AN(TI, T, 2); else if (nv <= 4) RLIS_AN(TI, T, 4); \
+                              else RLIS_AN(TI, T, 8); } while (0)
+        if (dtype == RLIS_F32) RLIS_AN_T(float, float);
+        else if (x_f32) RLIS_AN_T(float, bf16);
+        else RLIS_AN_T(bf16, bf16);
+#undef RLIS_AN_T
+#undef RLIS_AN
+        return RLIS_LAUNCH_CHECK();
+    }
     if (dtype == RLIS_F32)
         rlis_launch(act_norm_kernel<float, float>, n_tokens, THREADS, 0, stream, (const float*)x, x_stride, w,
                     (const float*)gate, gate_stride, (float*)out, out_stride, width, eps);
@@ -150,6 +320,15 @@ extern "C" int rlis_bias_act(const void* x, const float* b, void* out, long long
     const long long n = n_rows * width;
     if (n <= 0) return 0;
     if (act < 0 || act > 1) return RLIS_ERR_UNSUPPORTED;
+    if (width % 4 == 0 && (dtype == RLIS_F32 || dtype == RLIS_BF16)) {
+        const long long n4 = n / 4;
+        const unsigned vblocks = (unsigned)((n4 + 255) / 256 < 8192 ? (n4 + 255) / 256 : 8192);
+        if (dtype == RLIS_F32)
+            rlis_launch(bias_act_vec_kernel<float>, vblocks, 256, 0, stream, (const float*)x, b, (float*)out, n4, width, act);
+        else
+            rlis_launch(bias_act_vec_kernel<bf16>, vblocks, 256, 0, stream, (const bf16*)x, b, (bf16*)out, n4, width, act);
+        return RLIS_LAUNCH_CHECK();
+    }
     const unsigned blocks = (unsigned)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
     if (dtype == RLIS_F32)
         rlis_launch(bias_act_kernel<float>, blocks, 256, 0, stream, (const float*)x, b, (float*)out, n, width, act);

@@ -317,13 +317,46 @@ def latent_q_rope(q: torch.Tensor, qa: torch.Tensor, inv_freq: torch.Tensor, rot
     return qa
 
 
+LATENT_MMA = True          # debug switch "latent_mma": 0 takes the one-warp-a-row kernel for every size
+
+
+def latent_attention_takes_mma(dtype, dk: int, rank: int) -> bool:
+    """Whether the tensor-core kernels for attention over latent rows exist for these sizes."""
+    return bool(LATENT_MMA and dtype == torch.bfloat16 and _latent_mma_sizes(int(dk), int(rank)))
+
+
+@functools.lru_cache(maxsize=None)
+def _latent_mma_sizes(dk: int, rank: int) -> bool:
+    return bool(lib().rlis_attention_latent_mma_takes(dk, rank))
+
+
+@functools.lru_cache(maxsize=4096)
+def _latent_decode_pieces(n_decode: int, head_tiles: int, max_ctx: int, sms: int) -> tuple:
+    """(pieces, keys a piece) for decode attention over latent rows: a CTA takes 16 heads of one
+    token and holds an SM by its shared memory, so the context is cut until the CTAs about fill the
+    SMs, in pieces that are multiples of 64 keys and at least 256 long."""
+    ctas = max(1, n_decode * head_tiles)
+    want = max(1, min(sms // ctas, max_ctx // 256))
+    keys = -(-max_ctx // want)
+    keys = -(-keys // 64) * 64
+    return max(1, -(-max_ctx // keys)), keys
+
+
+def latent_decode_pieces(n_decode: int, n_heads: int, max_ctx: int) -> tuple:
+    return _latent_decode_pieces(int(n_decode), (int(n_heads) + 15) // 16, max(1, int(max_ctx)), num_sms())
+
+
 def attention_latent(qa: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, step, group: int, n_heads: int,
                      rank: int, page_size: int, scale: float, sinks: torch.Tensor | None = None,
                      window: int = 0) -> torch.Tensor:
     """Causal attention of every token of the step over its request's cached latent rows, which all
     heads share: score = scale * qa[t, h] . row, out[t, h] = sum of softmax weights times row[:rank].
     `sinks` float32 [nh]: exp(sink_h) joins the denominator of head h and nothing else.  qa float32
-    [T, nh dk]; cache [pages, 1, page_size, dk]; out [T, nh rank] in the cache's type."""
+    [T, nh dk]; cache [pages, 1, page_size, dk]; out [T, nh rank] in the cache's type.
+
+    bfloat16 with sizes the tensor-core kernels take: single decoded tokens go to the split decode
+    kernel, portions of prompts (the step's tile list) to the flash kernel.  Everything else, and all
+    of float32, to the kernel that takes one warp a (token, head)."""
     T = qa.shape[0]
     dk = cache.shape[-1]
     _req(qa, "qa", torch.float32, (T, n_heads * dk))
@@ -332,8 +365,32 @@ def attention_latent(qa: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, s
     if sinks is not None:
         _req(sinks, "sinks", torch.float32, (n_heads,))
     tables = step.block_tables[group]
-    check(lib().rlis_attention_latent(qa.data_ptr(), cache.data_ptr(), out.data_ptr(),
-                                      sinks.data_ptr() if sinks is not None else None,
+    sink_ptr = sinks.data_ptr() if sinks is not None else None
+    n_dec = getattr(step, "n_decode", 0)
+    n_tiles = getattr(step, "n_prefill_tiles", 0)
+    if latent_attention_takes_mma(cache.dtype, dk, rank) and (n_dec or n_tiles) and \
+            (n_tiles or not getattr(step, "n_prefill_tokens", 0)):
+        if n_dec:
+            pieces, keys = latent_decode_pieces(n_dec, n_heads, step.max_decode_ctx)
+            scratch = None
+            if pieces > 1:
+                scratch = step.buffer("latent_partial", (n_dec * ((n_heads + 15) // 16) * pieces * 16 * (rank + 2),),
+                                      torch.float32)
+            check(lib().rlis_attention_latent_decode(
+                qa.data_ptr(), cache.data_ptr(), out.data_ptr(), sink_ptr,
+                scratch.data_ptr() if scratch is not None else None, step.dec_rows.data_ptr(),
+                step.dec_seqs.data_ptr(), step.ctx_lens.data_ptr(), tables.data_ptr(), tables.shape[1], n_dec,
+                n_heads, dk, rank, page_size, float(scale), int(window), pieces, keys, _stream()),
+                "attention_latent_decode")
+            _count("attention_latent.decode.mma" + (".split" if pieces > 1 else ""))
+        if n_tiles:
+            check(lib().rlis_attention_latent_prefill(
+                qa.data_ptr(), cache.data_ptr(), out.data_ptr(), sink_ptr, step.prefill_tiles.data_ptr(), n_tiles,
+                step.cu_seqlens.data_ptr(), step.ctx_lens.data_ptr(), tables.data_ptr(), tables.shape[1], n_heads,
+                dk, rank, page_size, float(scale), int(window), _stream()), "attention_latent_prefill")
+            _count("attention_latent.prefill.mma")
+        return out
+    check(lib().rlis_attention_latent(qa.data_ptr(), cache.data_ptr(), out.data_ptr(), sink_ptr,
                                       step.seq_of_token.data_ptr(), step.positions.data_ptr(), tables.data_ptr(),
                                       None, tables.shape[1], T, n_heads, dk, rank, page_size, float(scale),
                                       int(window), _code(cache.dtype), _stream()), "attention_latent")
@@ -753,6 +810,7 @@ def _set_stream_rows(value):
 
 
 library.PYTHON_SWITCHES.update(fuse_norms=_set_flag("FUSE_NORMS"), prefill_tcgen05=_set_flag("PREFILL_TCGEN05"),
+                               latent_mma=_set_flag("LATENT_MMA"),
                                stream_rows=_set_stream_rows)
 
 

@@ -69,6 +69,21 @@ class LatentAttention(Mixer):
         s = self.spec
         return KVCacheSpec(1, s.kv_rank + s.rot_dim, s.window, values=False)
 
+    def _mma(self) -> bool:
+        s = self.spec
+        return ops.latent_attention_takes_mma(self.dtype, s.kv_rank + s.rot_dim, s.kv_rank)
+
+    @property
+    def prefill_tile(self):
+        # the flash kernel for prompt portions takes one tile of this many tokens a CTA
+        return ops.prefill_tile() if self.dtype == torch.bfloat16 and self._mma() else None
+
+    def launch_variant(self, step):
+        # decode attention cuts the context into pieces by the longest context of the step
+        if not step.n_decode or not self._mma():
+            return None
+        return ops.latent_decode_pieces(step.n_decode, self.spec.n_heads, step.max_decode_ctx)
+
     def forward(self, x, step, cache, state, writes_cache=True):
         s = self.spec
         T, H = x.shape[0], s.n_heads

@@ -44,7 +44,16 @@ CONFIGS = {
         layer("latent_attention", latent(4, 8, 12, 8, 16, 20, 0.25, dims=4, scaling=(2.0, 32, 4.0, 1.0)), 64),
     ]},
 }
-SEEDS = {"X": 3, "Y": 5}
+# latent rows that the tensor-core kernels take (multiples of 16 with a value width of 64 or 128): five heads
+# (one padded tile of 16) and eighteen (two tiles), a layer that reads another's rows
+WIDE = latent(5, 16, 32, 24, 48, 64, 0.2, dims=32, scaling=(16.0, 128, 16.0, 2.0))
+CONFIGS["Z"] = {"architecture": "Lasapel", "vocab": 157, "width": 80, "norm": {"eps": 1e-6}, "layers": [
+    layer("latent_attention", WIDE, 96),
+    layer("latent_attention", latent(18, 8, 16, 8, 32, 128, 0.3, dims=8), 48),
+    layer("lightning", {"heads": 2, "dim": 32, "vdim": 24, "decay": [0.97, 0.8]}),
+    layer("latent_attention", dict(WIDE, heads=2, dim=40, vdim=16, q_rank=16, kv_from=0), 64),
+]}
+SEEDS = {"X": 3, "Y": 5, "Z": 8}
 
 
 def tensor_shapes(cfg: dict) -> dict:
