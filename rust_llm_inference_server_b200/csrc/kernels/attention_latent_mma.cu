@@ -1,14 +1,15 @@
 // Attention over a cache of latent rows on the tensor cores (bfloat16; mma.sync m16n8k16 with
-// float32 sums), for prompt portions and for single decoded tokens.  The contract is that of
+// float32 sums), for prompt portions and for single decoded tokens.  The interface is that of
 // attention_latent.cu: a row [latent | rotated key part] of DK entries a token, shared by all heads;
 // score = scale * qa . row; values are the first DV entries of the same rows; an optional sink term
 // exp(sink_h) in a head's softmax denominator.
 //
 // A CTA of 8 warps works on 64-key stages brought to shared memory by 16-byte asynchronous copies,
 // double-buffered, rows padded by 8 entries.  A warp holds 16 query rows and HALF of the value
-// columns (DV / 2: its output sums are DV / 4 registers a thread), so two warps share their rows
-// and both form the scores.
+// columns (DV / 2: its output sums are DV / 4 registers a thread), so two warps share their rows.
 //   prompts: one head x 64 tokens a CTA; warp pair p takes tokens 16 p .. 16 p + 15 and every key.
+//            Each warp of a pair forms the scores of 32 of a stage's keys; the two exchange row
+//            maxima and the rounded weights through shared memory (three barriers of 64 threads).
 //   decode : 16 heads of one token a CTA, and one piece of its context; warp pair p takes keys
 //            16 p .. 16 p + 15 of every stage, and the four pairs' running (max, sum, output) are
 //            merged through shared memory at the end.  Several pieces of a context are merged by
@@ -22,6 +23,9 @@ namespace {
 constexpr int LF_THREADS = 256;
 constexpr int LF_BN = 64;                 // keys a stage
 constexpr float LOG2E = 1.4426950408889634f;
+
+// Barrier over the two warps of pair `p` (named barriers 1..4; 0 is __syncthreads).
+__device__ __forceinline__ void pair_barrier(int p) { asm volatile("bar.sync %0, 64;" ::"r"(p + 1) : "memory"); }
 
 struct LatentArgs {
     const float* qa;          // [T, nh, dk]
@@ -39,12 +43,12 @@ struct LatentArgs {
     float scale;
 };
 
-// PREFILL: 64 query rows a CTA, every warp pair sees all 64 keys of a stage (8 score tiles).
+// PREFILL: 64 query rows a CTA, every warp pair sees all 64 keys of a stage (4 score tiles a warp).
 // decode : 16 query rows a CTA, warp pair p sees keys 16 p .. 16 p + 15 of a stage (2 score tiles).
 template <int DV, bool PREFILL>
 __global__ __launch_bounds__(LF_THREADS) void latent_flash_kernel(const LatentArgs a) {
     pdl_wait();
-    constexpr int NT = PREFILL ? 8 : 2;          // score tiles (8 keys each) a warp forms a stage
+    constexpr int NT = PREFILL ? 4 : 2;          // score tiles (8 keys each) a warp forms a stage
     constexpr int QR = PREFILL ? 64 : 16;        // query rows a CTA
     constexpr int NO = DV / 16;                  // output tiles (8 columns each) a warp owns: half of DV / 8
     const int dk = a.dk, stride = dk + 8, ksteps = dk / 16, cpr = dk / 8;
@@ -143,7 +147,11 @@ __global__ __launch_bounds__(LF_THREADS) void latent_flash_kernel(const LatentAr
 #pragma unroll
         for (int e = 0; e < 4; ++e) oacc[n][e] = 0.f;
     const float scale_log2 = a.scale * LOG2E;
-    const int key_off = PREFILL ? 0 : pair * 16;             // this warp's keys within a stage
+    const int key_off = PREFILL ? half * 32 : pair * 16;     // the keys within a stage whose scores this warp forms
+    // prompts: where the two warps of a pair exchange maxima and weights, 8 words a lane
+    float* xch = reinterpret_cast<float*>(kbuf + (size_t)2 * LF_BN * stride);
+    float* xw = xch + ((pair * 2 + half) * 32 + lane) * 8;
+    const float* xo = xch + ((pair * 2 + (half ^ 1)) * 32 + lane) * 8;
     const int col0 = half * (DV / 2);                        // this warp's value columns
 
     int stage = 0;
@@ -156,7 +164,8 @@ __global__ __launch_bounds__(LF_THREADS) void latent_flash_kernel(const LatentAr
             cp_async_wait<0>();
         }
         __syncthreads();
-        const bf16* ks_ = kbuf + (size_t)stage * LF_BN * stride + (size_t)key_off * stride;
+        const bf16* kst = kbuf + (size_t)stage * LF_BN * stride;
+        const bf16* ks_ = kst + (size_t)key_off * stride;          // the keys whose scores this warp forms
 
         float sacc[NT][4];
 #pragma unroll
@@ -193,20 +202,62 @@ __global__ __launch_bounds__(LF_THREADS) void latent_flash_kernel(const LatentAr
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        if (PREFILL) {     // the other warp of the pair has the maxima of the stage's other 32 keys
+            xw[0] = mx0;
+            xw[1] = mx1;
+            pair_barrier(pair);
+            mx0 = fmaxf(mx0, xo[0]);
+            mx1 = fmaxf(mx1, xo[1]);
+            pair_barrier(pair);
+        }
         const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
         const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
         const float corr0 = exp2f(m_run[0] - ms0), corr1 = exp2f(m_run[1] - ms1);
+        // weights, rounded to bfloat16 as the A operand of the value product: [16 keys][4 registers]
+        uint32_t pown[NT / 2][4];
+#pragma unroll
+        for (int kk = 0; kk < NT / 2; ++kk) {
+            pown[kk][0] = pack_bf16(exp2f(sacc[2 * kk][0] - ms0), exp2f(sacc[2 * kk][1] - ms0));
+            pown[kk][1] = pack_bf16(exp2f(sacc[2 * kk][2] - ms1), exp2f(sacc[2 * kk][3] - ms1));
+            pown[kk][2] = pack_bf16(exp2f(sacc[2 * kk + 1][0] - ms0), exp2f(sacc[2 * kk + 1][1] - ms0));
+            pown[kk][3] = pack_bf16(exp2f(sacc[2 * kk + 1][2] - ms1), exp2f(sacc[2 * kk + 1][3] - ms1));
+        }
+        constexpr int PK = PREFILL ? 4 : 1;         // blocks of 16 keys in the value product
+        uint32_t pall[PK][4];
+        if (PREFILL) {
+            uint32_t* xwu = reinterpret_cast<uint32_t*>(xw);
+            const uint32_t* xou = reinterpret_cast<const uint32_t*>(xo);
+#pragma unroll
+            for (int kk = 0; kk < NT / 2; ++kk)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) xwu[kk * 4 + e] = pown[kk][e];
+            pair_barrier(pair);
+            uint32_t poth[NT / 2][4];
+#pragma unroll
+            for (int kk = 0; kk < NT / 2; ++kk)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) poth[kk][e] = xou[kk * 4 + e];
+#pragma unroll
+            for (int kk = 0; kk < PK; ++kk)          // blocks 0, 1 are the first warp's keys, 2, 3 the second's
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    pall[kk][e] = (kk >> 1) == half ? pown[kk % (NT / 2)][e] : poth[kk % (NT / 2)][e];
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pall[0][e] = pown[0][e];
+        }
+        // the row sums are taken over the rounded weights, in key order, so that both warps of a pair
+        // (and numerator and denominator) see the same numbers
         float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const float p0 = exp2f(sacc[nt][e] - ms0), p1 = exp2f(sacc[nt][2 + e] - ms1);
-                sacc[nt][e] = p0;
-                sacc[nt][2 + e] = p1;
-                ls0 += p0;
-                ls1 += p1;
-            }
+        for (int kk = 0; kk < PK; ++kk) {
+            const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pall[kk][0]));
+            const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pall[kk][1]));
+            const float2 a2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pall[kk][2]));
+            const float2 a3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pall[kk][3]));
+            ls0 += (a0.x + a0.y) + (a2.x + a2.y);
+            ls1 += (a1.x + a1.y) + (a3.x + a3.y);
+        }
         ls0 += __shfl_xor_sync(0xffffffffu, ls0, 1);
         ls0 += __shfl_xor_sync(0xffffffffu, ls0, 2);
         ls1 += __shfl_xor_sync(0xffffffffu, ls1, 1);
@@ -222,20 +273,16 @@ __global__ __launch_bounds__(LF_THREADS) void latent_flash_kernel(const LatentAr
             oacc[n][2] *= corr1;
             oacc[n][3] *= corr1;
         }
+        const bf16* vs_ = PREFILL ? kst : ks_;      // the keys whose values this warp sums
 #pragma unroll
-        for (int kk = 0; kk < NT / 2; ++kk) {
-            uint32_t pa[4];
-            pa[0] = pack_bf16(sacc[2 * kk][0], sacc[2 * kk][1]);
-            pa[1] = pack_bf16(sacc[2 * kk][2], sacc[2 * kk][3]);
-            pa[2] = pack_bf16(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
-            pa[3] = pack_bf16(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+        for (int kk = 0; kk < PK; ++kk) {
 #pragma unroll
             for (int n2 = 0; n2 < NO / 2; ++n2) {
                 uint32_t vb[4];
                 const int mat = lane >> 3;
-                ldmatrix_x4_trans(vb, ks_ + (kk * 16 + (mat & 1) * 8 + (lane & 7)) * stride + col0 + (n2 * 2 + (mat >> 1)) * 8);
-                mma_bf16_16816(oacc[2 * n2], pa, vb[0], vb[1]);
-                mma_bf16_16816(oacc[2 * n2 + 1], pa, vb[2], vb[3]);
+                ldmatrix_x4_trans(vb, vs_ + (kk * 16 + (mat & 1) * 8 + (lane & 7)) * stride + col0 + (n2 * 2 + (mat >> 1)) * 8);
+                mma_bf16_16816(oacc[2 * n2], pall[kk], vb[0], vb[1]);
+                mma_bf16_16816(oacc[2 * n2 + 1], pall[kk], vb[2], vb[3]);
             }
         }
         __syncthreads();
@@ -365,7 +412,8 @@ __global__ void latent_merge_kernel(const float* __restrict__ scratch, bf16* __r
 }
 
 template <bool PREFILL> size_t latent_smem_bytes(int dk, int dv) {
-    const size_t stages = (size_t)((PREFILL ? 64 : 16) + 2 * LF_BN) * (dk + 8) * sizeof(bf16);
+    const size_t stages = (size_t)((PREFILL ? 64 : 16) + 2 * LF_BN) * (dk + 8) * sizeof(bf16) +
+                          (PREFILL ? (size_t)LF_THREADS * 8 * sizeof(float) : 0);
     const size_t merge = PREFILL ? 0 : (size_t)16 * (dk + 8) * sizeof(bf16) + (4 * 16 * 2 + (size_t)16 * dv) * sizeof(float);
     return stages > merge ? stages : merge;
 }
@@ -373,7 +421,7 @@ template <bool PREFILL> size_t latent_smem_bytes(int dk, int dv) {
 template <int DV, bool PREFILL>
 int launch_latent(const LatentArgs& a, dim3 grid, int dv, cudaStream_t stream) {
     const size_t smem = latent_smem_bytes<PREFILL>(a.dk, dv);
-    if (smem > 227 * 1024) return RLIS_ERR_UNSUPPORTED;
+    if (smem > 227 * 1024) return RLIS_ERR_UNSUPPORTED;      // 232,448 bytes: the most a CTA can ask for
     static size_t allowed = 0;
     if (smem > allowed) {
         cudaFuncSetAttribute(latent_flash_kernel<DV, PREFILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -1,20 +1,22 @@
 // Linear attention with a per-head decay, as a recurrence over a float32 state:
 //
 //   q, k = silu(.) [heads, d]; v = silu(.) [heads, dv]           (from one fused projection's rows)
-//   S_t = decay_h * S_(t-1) + k_t v_t^T ;  o_t = S_t^T q_t        S [d, dv] per request and head
+//   S_t = decay_h * S_(t-1) + k_t v_t^T ;  o_t = S_t^T q_t        S [d, dv] per request and head (stored transposed)
 //
 // The state of a request lives in its state slot between steps; a request whose first token is in
 // this step starts from zero.  Columns of S evolve independently, so a CTA takes (request, head,
-// 32 columns): 8 threads share a column, each holding a contiguous eighth of its entries in
-// registers, and walk the request's tokens of this step in order.  Tokens are staged through shared
-// memory 16 at a time (silu applied once on the way in), the next 16 already on their way from
+// 16 columns): 16 threads share a column, each holding a contiguous sixteenth of its entries in
+// registers, and walk the request's tokens of this step in order; a column's partial sums are added
+// after each tile of tokens.  The state is stored column by column, [slot, head, dv, d], so that a
+// thread's entries are contiguous in memory.  Tokens are staged through shared
+// memory 16 (or 8) at a time (silu applied once on the way in), the next 16 already on their way from
 // global memory while the current ones are worked on.
 // Everything after the projection is float32; the order of every sum depends on d only.
 #include "common.cuh"
 #include <math.h>
 
 namespace {
-constexpr int COLS = 32, SLICES = 8, TOK = 16, MAX_E = 32;   // d up to 256
+constexpr int COLS = 16, SLICES = 16, MAX_E = 16;   // d up to 256
 constexpr int THREADS = COLS * SLICES;
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
@@ -28,26 +30,27 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
     float* __restrict__ state, const float* __restrict__ decay, const int* __restrict__ cu_seqlens,
     const int* __restrict__ ctx_lens, const int* __restrict__ state_slots, int nh, int d, int dv) {
     pdl_wait_and_trigger();
+    constexpr int TOK = E > 8 ? 8 : 16;           // tokens staged at a time (shared memory holds them)
     constexpr int DP = SLICES * E;                 // padded d
     constexpr int ES = E + 4;                      // a thread's share sits 4 floats apart from the next one's: no bank conflicts
     constexpr int DPS = SLICES * ES;
     __shared__ __align__(16) float qs[TOK * DPS];
     __shared__ __align__(16) float ks[TOK * DPS];
     __shared__ float vs[TOK * COLS];
-    __shared__ float os[TOK * COLS];
+    __shared__ __align__(16) float os[TOK * COLS * SLICES];   // a column's sixteen partial sums a token
     const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * COLS;
     const int row0 = cu_seqlens[b], n = cu_seqlens[b + 1] - row0;
     const int slice = threadIdx.x % SLICES, col = threadIdx.x / SLICES;
     const bool live = c0 + col < dv;
     const bool fresh = ctx_lens[b] - n == 0;      // the request starts in this step
     const int slot = state_slots[b];
-    float* S = state + ((size_t)slot * nh + h) * d * dv;
+    float* S = state + (((size_t)slot * nh + h) * dv + c0 + col) * d;    // this thread's column: d contiguous entries
     const float g = decay[h];
     float s[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) {
         const int i = slice * E + e;
-        s[e] = (!fresh && live && i < d) ? S[(size_t)i * dv + c0 + col] : 0.f;
+        s[e] = (!fresh && live && i < d) ? S[i] : 0.f;
     }
     // what one thread stages of q and k: element idx = threadIdx.x + j * THREADS of the [TOK][DP] tile
     constexpr int PER = TOK * DP / THREADS;
@@ -87,6 +90,7 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
         }
         __syncthreads();
         if (t0 + TOK < n) fetch(t0 + TOK);         // in flight while this tile is worked on
+#pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
             const float v = vs[tt * COLS + col];
             const float4* kr = reinterpret_cast<const float4*>(ks + tt * DPS + slice * ES);
@@ -104,23 +108,27 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
                 o[2] = fmaf(s[4 * e4 + 2], q4.z, o[2]);
                 o[3] = fmaf(s[4 * e4 + 3], q4.w, o[3]);
             }
-            float ot = (o[0] + o[1]) + (o[2] + o[3]);
-            ot += __shfl_xor_sync(0xffffffffu, ot, 1);
-            ot += __shfl_xor_sync(0xffffffffu, ot, 2);
-            ot += __shfl_xor_sync(0xffffffffu, ot, 4);
-            if (slice == 0) os[tt * COLS + col] = ot;
+            // the partial sums of a column are added after the tile: no shuffle chain per token
+            os[(tt * COLS + col) * SLICES + slice] = (o[0] + o[1]) + (o[2] + o[3]);
         }
         __syncthreads();
         for (int idx = threadIdx.x; idx < nt * COLS; idx += THREADS) {
             const int tt = idx / COLS, c = idx - tt * COLS;
-            if (c0 + c < dv) out[(size_t)(row0 + t0 + tt) * nh * dv + h * dv + c0 + c] = os[idx];
+            const float4* p4 = reinterpret_cast<const float4*>(os + idx * SLICES);
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < SLICES / 4; ++j) {
+                const float4 a = p4[j];
+                sum += (a.x + a.y) + (a.z + a.w);
+            }
+            if (c0 + c < dv) out[(size_t)(row0 + t0 + tt) * nh * dv + h * dv + c0 + c] = sum;
         }
     }
     if (live) {
 #pragma unroll
         for (int e = 0; e < E; ++e) {
             const int i = slice * E + e;
-            if (i < d) S[(size_t)i * dv + c0 + col] = s[e];
+            if (i < d) S[i] = s[e];
         }
     }
 }
@@ -134,8 +142,7 @@ int launch_scan(const T* proj, long long stride, int q_off, int k_off, int v_off
                                  v_off, out, state, decay, cu, ctx, slots, nh, d, dv)
     if (e <= 4) RLIS_SCAN(4);
     else if (e <= 8) RLIS_SCAN(8);
-    else if (e <= 16) RLIS_SCAN(16);
-    else RLIS_SCAN(32);
+    else RLIS_SCAN(16);
 #undef RLIS_SCAN
     return RLIS_LAUNCH_CHECK();
 }

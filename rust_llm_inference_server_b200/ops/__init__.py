@@ -402,12 +402,12 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: 
                    decay: torch.Tensor, step, n_heads: int, d: int, dv: int) -> torch.Tensor:
     """The decayed linear-attention recurrence over the step's tokens: per request and head
     S <- decay_h S + k v^T, o = S^T q, with q, k, v = silu of columns q_off.., k_off.., v_off.. of
-    `proj` [T, *].  `state` float32 [slots, nh, d, dv] holds S between steps (a request whose first
-    token is in this step starts from zero); out float32 [T, nh dv]."""
+    `proj` [T, *].  `state` float32 [slots, nh, dv, d] holds S, transposed, between steps (a request
+    whose first token is in this step starts from zero); out float32 [T, nh dv]."""
     T = proj.shape[0]
     _req(proj, "proj")
     _req(out, "out", torch.float32, (T, n_heads * dv))
-    _req(state, "state", torch.float32, (None, n_heads, d, dv))
+    _req(state, "state", torch.float32, (None, n_heads, dv, d))
     _req(decay, "decay", torch.float32, (n_heads,))
     if max(q_off, k_off) + n_heads * d > proj.shape[1] or v_off + n_heads * dv > proj.shape[1]:
         raise KernelError("lightning_scan: the column offsets reach beyond the projection's rows")

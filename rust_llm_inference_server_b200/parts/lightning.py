@@ -40,7 +40,7 @@ class LightningAttention(Mixer):
 
     def state_spec(self):
         s = self.spec
-        return StateSpec((s.n_heads, s.dim, s.v_dim), torch.float32)
+        return StateSpec((s.n_heads, s.v_dim, s.dim), torch.float32)     # S transposed: a column's entries are contiguous
 
     def forward(self, x, step, cache, state, writes_cache=True):
         s = self.spec

@@ -23,7 +23,7 @@ def test_describe_names_every_tensor_and_the_cache_plan():
     assert [(c.layer, c.cache, c.writes_cache) for c in m.calls] == [(0, 0, True), (1, 1, True), (2, 0, False), (3, 3, True)]
     assert m.cache_slot_specs[0].head_dim == 40 and m.cache_slot_specs[0].values is False
     assert m.cache_slot_specs[1] is None and m.cache_slot_specs[3] is None
-    assert [None if s is None else tuple(s.shape) for s in m.call_state_specs] == [None, (2, 24, 40), None, (3, 16, 16)]
+    assert [None if s is None else tuple(s.shape) for s in m.call_state_specs] == [None, (2, 40, 24), None, (3, 16, 16)]
     assert all(s is None or s.dtype == torch.float32 for s in m.call_state_specs)
 
 
@@ -117,14 +117,15 @@ def test_plain_sink_only_enters_the_denominator():
 
 def test_a_lost_state_a_missing_sink_or_a_key_one_off_would_show(model_root):
     """The weights of these tests make such faults large: the plain restatement with the fault
-    built in differs from the right one by far more than 0.08, the widest tolerance of the GPU tests."""
+    built in differs from the right one by far more than 0.045, the widest tolerance (a position's root-mean-square error) of the GPU tests."""
     d = U.make_dir(model_root, "X")
     cfg, w = U.read_config(d), U.plain_weights(d)
     toks = np.random.default_rng(1).integers(0, cfg["vocab"], size=120).tolist()
     right = P.forward(cfg, w, toks)
     no_sink = {k: (v - 40.0 if k.endswith("sink") else v) for k, v in w.items()}
-    assert np.abs(P.forward(cfg, no_sink, toks) - right).max() > 4 * 0.08
+    rms = lambda d: np.sqrt(np.mean(d * d, axis=-1)).max()
+    assert rms(P.forward(cfg, no_sink, toks) - right) > 4 * 0.045
     lost = P.forward(cfg, w, toks[60:])                     # the state and the keys of the first 60 tokens are gone
-    assert np.abs(lost - right[60:]).max() > 4 * 0.08
+    assert rms(lost - right[60:]) > 4 * 0.045
     dropped = P.forward(cfg, w, toks[:30] + toks[31:])      # one key missing, later positions one off
-    assert np.abs(dropped[30:] - right[31:]).max() > 4 * 0.08
+    assert rms(dropped[30:] - right[31:]) > 4 * 0.045

@@ -15,10 +15,18 @@ from tests.plain import lasapel_plain as P
 
 pytestmark = pytest.mark.gpu
 
-# Logits are about 1 in size.  float32: sums in another order than the plain float64 ones.
-# bfloat16: every product's inputs are rounded to 8 bits; attention here is peaked, which amplifies it.
-TOL = {"float32": 5e-5, "bfloat16": 0.08}
-TOL_BETWEEN = {"float32": 1e-5, "bfloat16": 0.08}
+# A position's error is the root mean square, over the vocabulary, of the difference of its logits
+# (which are about 1 in size).  float32: sums in another order than the plain float64 ones.  bfloat16:
+# every product's inputs are rounded to 8 bits, and attention here is peaked, which amplifies it: over
+# all positions the error is about 0.007, at the worst position about 0.03 with every kernel.
+TOL = {"float32": 2e-5, "bfloat16": 0.045}
+TOL_BETWEEN = {"float32": 1e-5, "bfloat16": 0.045}
+
+
+def position_error(a, b):
+    d = np.asarray(a, dtype=np.float64) - np.asarray(b, dtype=np.float64)
+    e = float(np.sqrt(np.mean(d * d)))
+    return e if np.isfinite(e) else float("inf")
 
 
 def dev(x, dtype=torch.float32):
@@ -43,8 +51,7 @@ def session(model_dir, dtype, max_tokens, page=16, max_live=4):
 def worst_difference(got, ref):
     worst, where = 0.0, None
     for (name, pos), row in got.items():
-        d = float(np.abs(row - ref[name][pos]).max())
-        d = d if np.isfinite(d) else float("inf")
+        d = position_error(row, ref[name][pos])
         if d >= worst:
             worst, where = d, (name, pos)
     return worst, where
@@ -288,7 +295,7 @@ def test_tensor_core_attention_over_latents(H, rank, rot, window, use_sinks):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,d,dv", [(2, 24, 40), (1, 8, 48), (3, 128, 16)])
+@pytest.mark.parametrize("H,d,dv", [(2, 24, 40), (1, 8, 48), (3, 128, 16), (2, 200, 8)])
 def test_decayed_recurrence_carries_its_state(dtype, H, d, dv):
     from rust_llm_inference_server_b200 import ops
     rng = np.random.default_rng(d)
@@ -296,7 +303,7 @@ def test_decayed_recurrence_carries_its_state(dtype, H, d, dv):
     lead, width = 3, 2 * H * d + H * dv
     lens = {0: [5, 1, 1, 19, 2], 1: [1, 33, 1, 1, 4]}             # two requests in portions
     toks = {b: rng.standard_normal((sum(l), lead + width)) for b, l in lens.items()}
-    state = torch.full((4, H, d, dv), 7.0, device="cuda")        # slots hold leftovers of earlier requests
+    state = torch.full((4, H, dv, d), 7.0, device="cuda")           # S is kept transposed        # slots hold leftovers of earlier requests
     slots, done, got = {0: 2, 1: 0}, {0: 0, 1: 0}, {0: [], 1: []}
     for k in range(5):
         order = [0, 1] if k % 2 == 0 else [1, 0]
@@ -324,7 +331,7 @@ def test_decayed_recurrence_carries_its_state(dtype, H, d, dv):
                 want[t, h] = S.T @ q[t, h]
         np.testing.assert_allclose(np.concatenate(got[b]).reshape(-1, H, dv), want, rtol=2e-5, atol=2e-4)
         # the state left in the slot is the last S, in float32
-        np.testing.assert_allclose(state[slots[b], H - 1].cpu().numpy(), S, rtol=2e-5, atol=2e-4)
+        np.testing.assert_allclose(state[slots[b], H - 1].cpu().numpy(), S.T, rtol=2e-5, atol=2e-4)
     assert float((state[1] - 7.0).abs().max()) == 0.0 and float((state[3] - 7.0).abs().max()) == 0.0
 
 
@@ -383,7 +390,7 @@ def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, page, lens
         worst, where = worst_difference(results[fam], ref)
         assert worst <= TOL[dtype], f"{which} {dtype} {fam} vs plain: {worst} at {where}"
     for fam in ("decode", "chunks", "mixed", "mixed2"):
-        worst = max(float(np.abs(v - results["whole"][k]).max()) for k, v in results[fam].items())
+        worst = max(position_error(v, results["whole"][k]) for k, v in results[fam].items())
         assert worst <= TOL_BETWEEN[dtype], f"{which} {dtype}: {fam} differs from whole by {worst}"
     fast = dtype == "bfloat16" and which == "Z"
     for k in (("attention_latent.decode.mma", "attention_latent.prefill.mma") if fast else ("attention_latent",)) + ("lightning_scan", "latent_kv_store", "latent_q_rope", "post_norm_residual",
