@@ -24,12 +24,12 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z));
 // E = entries of a column that one thread holds: ceil(d / 8), rounded up to a multiple of 4 so that a
 // thread reads its share of k and q from shared memory in 16-byte vectors.  Thread `slice` owns the
 // entries slice * E .. slice * E + E - 1 (those at or beyond d stay zero).
-template <typename T, int E>
+template <typename T, int E, bool SILU>
 __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
     const T* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, float* __restrict__ out,
     float* __restrict__ state, const float* __restrict__ decay, const int* __restrict__ cu_seqlens,
     const int* __restrict__ ctx_lens, const int* __restrict__ state_slots, int nh, int d, int dv) {
-    pdl_wait_and_trigger();
+    pdl_wait();     // (the next kernel is let in at the end: this one runs long on few warps)
     constexpr int TOK = E > 8 ? 8 : 16;           // tokens staged at a time (shared memory holds them)
     constexpr int DP = SLICES * E;                 // padded d
     constexpr int ES = E + 4;                      // a thread's share sits 4 floats apart from the next one's: no bank conflicts
@@ -80,13 +80,13 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
         for (int j = 0; j < PER; ++j) {
             const int idx = threadIdx.x + j * THREADS, tt = idx / DP, i = idx - tt * DP;
             const int at = tt * DPS + (i / E) * ES + i % E;
-            qs[at] = silu_f(rq[j]);                // silu(0) = 0 keeps the padding zero
-            ks[at] = silu_f(rk[j]);
+            qs[at] = SILU ? silu_f(rq[j]) : rq[j];  // silu(0) = 0 keeps the padding zero
+            ks[at] = SILU ? silu_f(rk[j]) : rk[j];
         }
 #pragma unroll
         for (int j = 0; j < (TOK * COLS + THREADS - 1) / THREADS; ++j) {
             const int idx = threadIdx.x + j * THREADS;
-            if (idx < TOK * COLS) vs[idx] = silu_f(rv[j]);
+            if (idx < TOK * COLS) vs[idx] = SILU ? silu_f(rv[j]) : rv[j];
         }
         __syncthreads();
         if (t0 + TOK < n) fetch(t0 + TOK);         // in flight while this tile is worked on
@@ -131,14 +131,29 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
             if (i < d) S[i] = s[e];
         }
     }
+    pdl_trigger();
 }
 
+// out[t, :] = silu(x[t, :width]) in float32: the activation applied once for every CTA of the scan
+// that reads it (long steps; a short step applies it while staging).
 template <typename T>
+__global__ void silu_rows_kernel(const T* __restrict__ x, long long stride, float* __restrict__ out, int width) {
+    // The scan that follows has few CTAs and wants one to an SM: let in early, while this grid still fills
+    // the SMs, its CTAs would land several to an SM wherever room appears first.  So it is let in at the end.
+    pdl_wait();
+    const T* xr = x + (size_t)blockIdx.x * stride;
+    float* orow = out + (size_t)blockIdx.x * width;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x)
+        orow[c] = silu_f(to_f<T>(xr[c]));
+    pdl_trigger();
+}
+
+template <typename T, bool SILU>
 int launch_scan(const T* proj, long long stride, int q_off, int k_off, int v_off, float* out, float* state,
                 const float* decay, const int* cu, const int* ctx, const int* slots, dim3 grid, int nh, int d, int dv,
                 cudaStream_t stream) {
     const int e = (d + SLICES - 1) / SLICES;
-#define RLIS_SCAN(E) rlis_launch(lightning_scan_kernel<T, E>, grid, THREADS, 0, stream, proj, stride, q_off, k_off, \
+#define RLIS_SCAN(E) rlis_launch(lightning_scan_kernel<T, E, SILU>, grid, THREADS, 0, stream, proj, stride, q_off, k_off, \
                                  v_off, out, state, decay, cu, ctx, slots, nh, d, dv)
     if (e <= 4) RLIS_SCAN(4);
     else if (e <= 8) RLIS_SCAN(8);
@@ -151,16 +166,31 @@ int launch_scan(const T* proj, long long stride, int q_off, int k_off, int v_off
 extern "C" int rlis_lightning_scan(const void* proj, long long stride, int q_off, int k_off, int v_off, float* out,
                                    float* state, const float* decay, const int* cu_seqlens, const int* ctx_lens,
                                    const int* state_slots, int n_seqs, int nh, int d, int dv, int dtype,
-                                   cudaStream_t stream) {
+                                   float* activated, int n_tokens, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (d <= 0 || d > SLICES * MAX_E || dv <= 0 || nh <= 0 || nh > 65535) return RLIS_ERR_UNSUPPORTED;
     dim3 grid(n_seqs, nh, (dv + COLS - 1) / COLS);
     if (grid.z > 65535) return RLIS_ERR_UNSUPPORTED;
+    if (activated != nullptr) {
+        // long steps: silu once into `activated` (float32 [tokens, width], width = the columns up to the end
+        // of v, which must start at q_off = 0), then the scan reads that
+        const int width = v_off + nh * dv;
+        if (q_off != 0 || k_off > v_off || n_tokens <= 0) return RLIS_ERR_UNSUPPORTED;
+        const dim3 blocks(n_tokens, (width + 1023) / 1024 < 8 ? (width + 1023) / 1024 : 8);
+        if (dtype == RLIS_F32)
+            rlis_launch(silu_rows_kernel<float>, blocks, 256, 0, stream, (const float*)proj, stride, activated, width);
+        else if (dtype == RLIS_BF16)
+            rlis_launch(silu_rows_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)proj, stride, activated, width);
+        else
+            return RLIS_ERR_UNSUPPORTED;
+        return launch_scan<float, false>(activated, (long long)width, q_off, k_off, v_off, out, state, decay, cu_seqlens,
+                                         ctx_lens, state_slots, grid, nh, d, dv, stream);
+    }
     if (dtype == RLIS_F32)
-        return launch_scan((const float*)proj, stride, q_off, k_off, v_off, out, state, decay, cu_seqlens, ctx_lens,
-                           state_slots, grid, nh, d, dv, stream);
+        return launch_scan<float, true>((const float*)proj, stride, q_off, k_off, v_off, out, state, decay, cu_seqlens,
+                                        ctx_lens, state_slots, grid, nh, d, dv, stream);
     if (dtype == RLIS_BF16)
-        return launch_scan((const bf16*)proj, stride, q_off, k_off, v_off, out, state, decay, cu_seqlens, ctx_lens,
-                           state_slots, grid, nh, d, dv, stream);
+        return launch_scan<bf16, true>((const bf16*)proj, stride, q_off, k_off, v_off, out, state, decay, cu_seqlens,
+                                       ctx_lens, state_slots, grid, nh, d, dv, stream);
     return RLIS_ERR_UNSUPPORTED;
 }

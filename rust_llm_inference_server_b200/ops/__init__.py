@@ -210,9 +210,11 @@ def per_head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torc
         return gemm_f32_batched(a, w, out)
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not a.is_cuda:
         raise KernelError(f"per_head_linear: expected float32 or bfloat16 operands on the device, got {a.dtype}, {w.dtype}")
-    res = torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out_dtype=out.dtype) if out.dtype != a.dtype \
-        else torch.bmm(a.transpose(0, 1), w.transpose(1, 2))
-    out.copy_(res.transpose(0, 1))
+    # [H, T, N] view of `out` (rows H * width apart, heads one head's width apart): the library writes it in place
+    if out.dtype != a.dtype:
+        torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out_dtype=out.dtype, out=out.transpose(0, 1))
+    else:
+        torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
     return out
 
 
@@ -398,6 +400,9 @@ def attention_latent(qa: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, s
     return out
 
 
+LIGHTNING_SILU_PASS_TOKENS = 64
+
+
 def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torch.Tensor, state: torch.Tensor,
                    decay: torch.Tensor, step, n_heads: int, d: int, dv: int) -> torch.Tensor:
     """The decayed linear-attention recurrence over the step's tokens: per request and head
@@ -411,11 +416,17 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: 
     _req(decay, "decay", torch.float32, (n_heads,))
     if max(q_off, k_off) + n_heads * d > proj.shape[1] or v_off + n_heads * dv > proj.shape[1]:
         raise KernelError("lightning_scan: the column offsets reach beyond the projection's rows")
+    # Steps of many tokens: silu is applied once, into a float32 buffer that every CTA of a head then
+    # reads (each would otherwise apply it to the head's q and k again).
+    activated = None
+    if T >= LIGHTNING_SILU_PASS_TOKENS and q_off == 0 and k_off <= v_off and hasattr(step, "buffer"):
+        activated = step.buffer("lightning_act", (T, v_off + n_heads * dv), torch.float32)
     check(lib().rlis_lightning_scan(proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, out.data_ptr(),
                                     state.data_ptr(), decay.data_ptr(), step.cu_seqlens.data_ptr(),
                                     step.ctx_lens.data_ptr(), step.state_slots.data_ptr(), step.n_seqs, n_heads, d,
-                                    dv, _code(proj.dtype), _stream()), "lightning_scan")
-    _count("lightning_scan")
+                                    dv, _code(proj.dtype), activated.data_ptr() if activated is not None else None,
+                                    T, _stream()), "lightning_scan")
+    _count("lightning_scan" + (".silu_pass" if activated is not None else ""))
     return out
 
 

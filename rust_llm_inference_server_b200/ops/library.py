@@ -38,7 +38,7 @@ SIGNATURES = {
     "rlis_attention_latent_mma_takes": [I, I],
     "rlis_attention_latent_prefill": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
     "rlis_attention_latent_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
-    "rlis_lightning_scan": [P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, I, P],
+    "rlis_lightning_scan": [P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, I, P, I, P],
     "rlis_rope_cache": [P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "rlis_attention_generic": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "rlis_attention_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
