@@ -4,7 +4,7 @@
 // value sum is taken over the latent part of the rows; the caller applies W_uv afterwards.
 //
 //   latent_kv_store : row = [ z[:r] / sqrt(mean(z[:r]^2) + eps) * w | rotate(z[r:]) ] -> paged cache
-//   latent_q_rope   : qa[t, h, r:] = rotate(q[t, h, d:]) in float32
+//   latent_q_rope   : qa[t, h, r:] = rotate(q[t, h, d:]), float32 (or bfloat16 for the tensor-core kernels)
 //   attention_latent: softmax over keys 0..pos (or the last `window`), optionally with one more
 //                     term exp(sink_h) in the denominator that has no value
 //
@@ -57,8 +57,8 @@ __global__ __launch_bounds__(128) void latent_kv_store_kernel(
     }
 }
 
-template <typename T>
-__global__ void latent_q_rope_kernel(const T* __restrict__ q, float* __restrict__ qa,
+template <typename T, typename TO>
+__global__ void latent_q_rope_kernel(const T* __restrict__ q, TO* __restrict__ qa,
                                      const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                      int n_heads, int d_plain, int rot_width, int rot_dims, int rank, float mag,
                                      long long total) {
@@ -80,7 +80,7 @@ __global__ void latent_q_rope_kernel(const T* __restrict__ q, float* __restrict_
         const float a = to_f<T>(src[j]), b = to_f<T>(src[j + half]);
         v = i < half ? rope_first(a, b, c, s) : rope_second(a, b, c, s);
     }
-    qa[th * (rank + rot_width) + rank + i] = v;
+    qa[th * (rank + rot_width) + rank + i] = from_f<TO>(v);
 }
 
 // One warp per (token, head).
@@ -191,19 +191,23 @@ extern "C" int rlis_latent_kv_store(const void* z, long long z_stride, const flo
     return RLIS_LAUNCH_CHECK();
 }
 
-extern "C" int rlis_latent_q_rope(const void* q, float* qa, const float* inv_freq, const int* positions,
+// out_bf16 != 0: qa is bfloat16 (for the tensor-core attention kernels), else float32.
+extern "C" int rlis_latent_q_rope(const void* q, void* qa, const float* inv_freq, const int* positions,
                                   int n_tokens, int n_heads, int d_plain, int rot_width, int rot_dims, int rank,
-                                  float mag, int dtype, cudaStream_t stream) {
+                                  float mag, int dtype, int out_bf16, cudaStream_t stream) {
     const long long total = (long long)n_tokens * n_heads * rot_width;
     if (total <= 0) return 0;
     if (rot_dims < 0 || rot_dims > rot_width || rot_dims % 2) return RLIS_ERR_UNSUPPORTED;
     const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dtype == RLIS_F32)
-        rlis_launch(latent_q_rope_kernel<float>, blocks, 256, 0, stream, (const float*)q, qa, inv_freq, positions,
-                    n_heads, d_plain, rot_width, rot_dims, rank, mag, total);
+    if (dtype == RLIS_F32 && !out_bf16)
+        rlis_launch(latent_q_rope_kernel<float, float>, blocks, 256, 0, stream, (const float*)q, (float*)qa, inv_freq,
+                    positions, n_heads, d_plain, rot_width, rot_dims, rank, mag, total);
+    else if (dtype == RLIS_BF16 && !out_bf16)
+        rlis_launch(latent_q_rope_kernel<bf16, float>, blocks, 256, 0, stream, (const bf16*)q, (float*)qa, inv_freq,
+                    positions, n_heads, d_plain, rot_width, rot_dims, rank, mag, total);
     else if (dtype == RLIS_BF16)
-        rlis_launch(latent_q_rope_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)q, qa, inv_freq, positions,
-                    n_heads, d_plain, rot_width, rot_dims, rank, mag, total);
+        rlis_launch(latent_q_rope_kernel<bf16, bf16>, blocks, 256, 0, stream, (const bf16*)q, (bf16*)qa, inv_freq,
+                    positions, n_heads, d_plain, rot_width, rot_dims, rank, mag, total);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

@@ -10,25 +10,26 @@
 //   prompts: one head x 64 tokens a CTA; warp pair p takes tokens 16 p .. 16 p + 15 and every key.
 //            Each warp of a pair forms the scores of 32 of a stage's keys; the two exchange row
 //            maxima and the rounded weights through shared memory (three barriers of 64 threads).
-//   decode : 16 heads of one token a CTA, and one piece of its context; warp pair p takes keys
-//            16 p .. 16 p + 15 of every stage, and the four pairs' running (max, sum, output) are
-//            merged through shared memory at the end.  Several pieces of a context are merged by
+//   decode : 16 heads of one token a CTA (two warp pairs, stages of 32 keys: two CTAs fit an SM), and
+//            one piece of its context; warp pair p takes keys 16 p .. 16 p + 15 of every stage, and the
+//            pairs' running (max, sum, output) are merged through shared memory at the end.  Several pieces of a context are merged by
 //            a second small kernel.
-// Queries arrive as float32 and are rounded to bfloat16 once, into shared memory.
+// Queries arrive as bfloat16 (copied asynchronously) or as float32 (rounded once, into shared memory).
 #include "common.cuh"
 #include "mma_utils.cuh"
 #include <math.h>
 
 namespace {
-constexpr int LF_THREADS = 256;
-constexpr int LF_BN = 64;                 // keys a stage
+// prompts: 4 warp pairs (256 threads), 64 keys a stage; decode: 2 pairs (128 threads), 32 keys a stage, so
+// that two CTAs fit an SM's shared memory at the widest rows
+constexpr int LF_BN_MAX = 64;
 constexpr float LOG2E = 1.4426950408889634f;
 
 // Barrier over the two warps of pair `p` (named barriers 1..4; 0 is __syncthreads).
 __device__ __forceinline__ void pair_barrier(int p) { asm volatile("bar.sync %0, 64;" ::"r"(p + 1) : "memory"); }
 
 struct LatentArgs {
-    const float* qa;          // [T, nh, dk]
+    const void* qa;           // [T, nh, dk], float32 or (q_bf16) bfloat16
     const bf16* cache;        // [pages, 1, page, dk]
     bf16* out;                // [T, nh, dv]
     const float* sinks;       // [nh] or null
@@ -41,13 +42,17 @@ struct LatentArgs {
     float* scratch;           // decode, several pieces: [n_dec][head tiles][pieces][16][dv + 2]
     int max_blocks, nh, dk, page_size, window, pieces, piece_keys;
     float scale;
+    int q_bf16;
 };
 
 // PREFILL: 64 query rows a CTA, every warp pair sees all 64 keys of a stage (4 score tiles a warp).
 // decode : 16 query rows a CTA, warp pair p sees keys 16 p .. 16 p + 15 of a stage (2 score tiles).
 template <int DV, bool PREFILL>
-__global__ __launch_bounds__(LF_THREADS) void latent_flash_kernel(const LatentArgs a) {
+__global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const LatentArgs a) {
     pdl_wait();
+    constexpr int PAIRS = PREFILL ? 4 : 2;
+    constexpr int LF_THREADS = PAIRS * 64;
+    constexpr int LF_BN = PAIRS * 16;            // keys a stage
     constexpr int NT = PREFILL ? 4 : 2;          // score tiles (8 keys each) a warp forms a stage
     constexpr int QR = PREFILL ? 64 : 16;        // query rows a CTA
     constexpr int NO = DV / 16;                  // output tiles (8 columns each) a warp owns: half of DV / 8
@@ -85,32 +90,58 @@ __global__ __launch_bounds__(LF_THREADS) void latent_flash_kernel(const LatentAr
     }
     const int* table = a.block_tables + (size_t)b * a.max_blocks;
 
-    // queries -> shared memory, rounded to bfloat16; rows beyond the tile (or the heads) are zero
-    for (int idx = threadIdx.x; idx < QR * (dk / 2); idx += LF_THREADS) {
-        const int r = idx / (dk / 2), j = (idx - r * (dk / 2)) * 2;
-        float2 v = make_float2(0.f, 0.f);
-        if (PREFILL) {
-            if (r < n_q_rows) v = *reinterpret_cast<const float2*>(a.qa + ((size_t)(q_row0 + r) * nh + head0) * dk + j);
-        } else {
-            if (head0 + r < nh) v = *reinterpret_cast<const float2*>(a.qa + ((size_t)q_row0 * nh + head0 + r) * dk + j);
+    // queries -> shared memory: bfloat16 ones by 16-byte asynchronous copies (they join the first stage's
+    // group), float32 ones rounded once on the way; rows beyond the tile (or the heads) are zero
+    if (a.q_bf16) {
+        const bf16* qsrc = reinterpret_cast<const bf16*>(a.qa);
+        for (int idx = threadIdx.x; idx < QR * cpr; idx += LF_THREADS) {
+            const int r = idx / cpr, c16 = idx - r * cpr;
+            const bool valid = PREFILL ? r < n_q_rows : head0 + r < nh;
+            const size_t row = PREFILL ? (size_t)(q_row0 + (valid ? r : 0)) * nh + head0
+                                       : (size_t)q_row0 * nh + head0 + (valid ? r : 0);
+            cp_async16(qs + r * stride + c16 * 8, qsrc + row * dk + c16 * 8, valid);
         }
-        *reinterpret_cast<uint32_t*>(qs + r * stride + j) = pack_bf16(v.x, v.y);
+    } else {
+        const float* qsrc = reinterpret_cast<const float*>(a.qa);
+        for (int idx = threadIdx.x; idx < QR * (dk / 2); idx += LF_THREADS) {
+            const int r = idx / (dk / 2), j = (idx - r * (dk / 2)) * 2;
+            float2 v = make_float2(0.f, 0.f);
+            if (PREFILL) {
+                if (r < n_q_rows) v = *reinterpret_cast<const float2*>(qsrc + ((size_t)(q_row0 + r) * nh + head0) * dk + j);
+            } else {
+                if (head0 + r < nh) v = *reinterpret_cast<const float2*>(qsrc + ((size_t)q_row0 * nh + head0 + r) * dk + j);
+            }
+            *reinterpret_cast<uint32_t*>(qs + r * stride + j) = pack_bf16(v.x, v.y);
+        }
     }
 
     const int kt0 = k_lo / LF_BN, kt1 = k_hi > k_lo ? (k_hi + LF_BN - 1) / LF_BN : kt0;
+    if (kt0 >= kt1) {      // no key at all: nothing will wait for the queries' copies
+        cp_async_commit();
+        cp_async_wait<0>();
+    }
     const int page_size = a.page_size;
-    // four threads copy a key's row, 16 bytes each in turn; a thread looks its key's page up once a stage
-    const int key_in = threadIdx.x >> 2, sub = threadIdx.x & 3;
+    // A warp copies 8 of a stage's keys: lanes 0..7 look the keys' pages up (one load each), the row
+    // addresses go round by shuffle, and the 32 lanes copy a row in runs of 512 contiguous bytes.
     auto issue = [&](int kt, int stage) {
-        const int key = kt * LF_BN + key_in;
-        const bool valid = key < k_hi && key >= k_lo;
-        const bf16* src = a.cache;
-        if (valid) {
-            const int pi = key / page_size;
-            src += ((size_t)table[pi] * page_size + (key - pi * page_size)) * dk;
+        const int key0 = kt * LF_BN + warp * 8;
+        long long my_off = -1;
+        if (lane < 8) {
+            const int key = key0 + lane;
+            if (key < k_hi && key >= k_lo) {
+                const int pi = key / page_size;
+                my_off = ((long long)table[pi] * page_size + (key - pi * page_size)) * dk;
+            }
         }
-        bf16* dst = kbuf + ((size_t)stage * LF_BN + key_in) * stride;
-        for (int c16 = sub; c16 < cpr; c16 += 4) cp_async16(dst + c16 * 8, src + c16 * 8, valid);
+        bf16* dst0 = kbuf + ((size_t)stage * LF_BN + warp * 8) * stride;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const long long off = __shfl_sync(0xffffffffu, my_off, k);
+            const bool valid = off >= 0;
+            const bf16* src = a.cache + (valid ? off : 0);
+            bf16* dst = dst0 + k * stride;
+            for (int c16 = lane; c16 < cpr; c16 += 32) cp_async16(dst + c16 * 8, src + c16 * 8, valid);
+        }
         cp_async_commit();
     };
 
@@ -311,7 +342,7 @@ __global__ __launch_bounds__(LF_THREADS) void latent_flash_kernel(const LatentAr
     // decode: merge the four warp pairs (their keys differ) through shared memory, which the key
     // stages no longer need: ml [4 pairs][16 rows][2], then sums [16][DV] float32
     float* ml = reinterpret_cast<float*>(kbuf);
-    float* osum = ml + 4 * 16 * 2;
+    float* osum = ml + PAIRS * 16 * 2;
     if (half == 0 && c == 0) {
         ml[(pair * 16 + g) * 2] = m_run[0];
         ml[(pair * 16 + g) * 2 + 1] = l_run[0];
@@ -321,19 +352,19 @@ __global__ __launch_bounds__(LF_THREADS) void latent_flash_kernel(const LatentAr
     __syncthreads();
     float mg0 = -INFINITY, mg1 = -INFINITY;
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
+    for (int p = 0; p < PAIRS; ++p) {
         mg0 = fmaxf(mg0, ml[(p * 16 + g) * 2]);
         mg1 = fmaxf(mg1, ml[(p * 16 + g + 8) * 2]);
     }
     const float ms0 = mg0 == -INFINITY ? 0.f : mg0, ms1 = mg1 == -INFINITY ? 0.f : mg1;
     float lg0 = 0.f, lg1 = 0.f;
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
+    for (int p = 0; p < PAIRS; ++p) {
         lg0 += ml[(p * 16 + g) * 2 + 1] * exp2f(ml[(p * 16 + g) * 2] - ms0);
         lg1 += ml[(p * 16 + g + 8) * 2 + 1] * exp2f(ml[(p * 16 + g + 8) * 2] - ms1);
     }
     const float w0 = exp2f(m_run[0] - ms0), w1 = exp2f(m_run[1] - ms1);
-    for (int p = 0; p < 4; ++p) {
+    for (int p = 0; p < PAIRS; ++p) {
         if (pair == p) {
 #pragma unroll
             for (int n = 0; n < NO; ++n) {
@@ -389,32 +420,49 @@ __global__ __launch_bounds__(LF_THREADS) void latent_flash_kernel(const LatentAr
     pdl_trigger();
 }
 
-// One CTA a (decoded token, head): folds the pieces' (max, sum, output) into the output row.
+// One CTA a (decoded token, head): folds the pieces' (max, sum, output) into the output row.  The
+// pieces' weights exp2(max_p - max) are worked out once, by one thread a piece.
 template <int DV>
 __global__ void latent_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out,
                                     const int* __restrict__ dec_rows, int nh, int head_tiles, int pieces) {
     pdl_wait_and_trigger();
+    extern __shared__ float wts[];                 // [pieces] weights, then [pieces] scratch
+    __shared__ float red[33];
     const int di = blockIdx.y, h = blockIdx.x;
     const float* part = scratch + (((size_t)di * head_tiles + h / 16) * pieces) * 16 * (DV + 2) + (size_t)(h % 16) * (DV + 2);
     const size_t piece_stride = (size_t)16 * (DV + 2);
     float m = -INFINITY;
-    for (int p = 0; p < pieces; ++p) m = fmaxf(m, part[p * piece_stride + DV]);
+    for (int p = threadIdx.x; p < pieces; p += blockDim.x) {
+        wts[pieces + p] = part[p * piece_stride + DV];
+        m = fmaxf(m, wts[pieces + p]);
+    }
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = -INFINITY;
+    for (int w = 0; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, red[w]);
     const float ms = m == -INFINITY ? 0.f : m;
     float l = 0.f;
-    for (int p = 0; p < pieces; ++p) l += part[p * piece_stride + DV + 1] * exp2f(part[p * piece_stride + DV] - ms);
+    for (int p = threadIdx.x; p < pieces; p += blockDim.x) {
+        const float w = exp2f(wts[pieces + p] - ms);
+        wts[p] = w;
+        l += part[p * piece_stride + DV + 1] * w;
+    }
+    l = block_sum(l, red);                         // (its barriers also publish the weights)
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     bf16* o = out + ((size_t)dec_rows[di] * nh + h) * DV;
     for (int col = threadIdx.x; col < DV; col += blockDim.x) {
         float acc = 0.f;
-        for (int p = 0; p < pieces; ++p) acc += part[p * piece_stride + col] * exp2f(part[p * piece_stride + DV] - ms);
+#pragma unroll 8
+        for (int p = 0; p < pieces; ++p) acc = fmaf(part[p * piece_stride + col], wts[p], acc);
         o[col] = __float2bfloat16_rn(acc * inv);
     }
 }
 
 template <bool PREFILL> size_t latent_smem_bytes(int dk, int dv) {
-    const size_t stages = (size_t)((PREFILL ? 64 : 16) + 2 * LF_BN) * (dk + 8) * sizeof(bf16) +
-                          (PREFILL ? (size_t)LF_THREADS * 8 * sizeof(float) : 0);
-    const size_t merge = PREFILL ? 0 : (size_t)16 * (dk + 8) * sizeof(bf16) + (4 * 16 * 2 + (size_t)16 * dv) * sizeof(float);
+    const size_t stages = (size_t)((PREFILL ? 64 : 16) + 2 * (PREFILL ? 64 : 32)) * (dk + 8) * sizeof(bf16) +
+                          (PREFILL ? (size_t)256 * 8 * sizeof(float) : 0);
+    const size_t merge = PREFILL ? 0 : (size_t)16 * (dk + 8) * sizeof(bf16) + (2 * 16 * 2 + (size_t)16 * dv) * sizeof(float);
     return stages > merge ? stages : merge;
 }
 
@@ -427,7 +475,7 @@ int launch_latent(const LatentArgs& a, dim3 grid, int dv, cudaStream_t stream) {
         cudaFuncSetAttribute(latent_flash_kernel<DV, PREFILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         allowed = smem;
     }
-    rlis_launch(latent_flash_kernel<DV, PREFILL>, grid, LF_THREADS, smem, stream, a);
+    rlis_launch(latent_flash_kernel<DV, PREFILL>, grid, PREFILL ? 256 : 128, smem, stream, a);
     return RLIS_LAUNCH_CHECK();
 }
 }  // namespace
@@ -439,7 +487,7 @@ extern "C" int rlis_attention_latent_mma_takes(int dk, int dv) {
     return latent_smem_bytes<true>(dk, dv) <= 227 * 1024 ? 1 : 0;
 }
 
-extern "C" int rlis_attention_latent_prefill(const float* qa, const void* cache, void* out, const float* sinks,
+extern "C" int rlis_attention_latent_prefill(const void* qa, int q_bf16, const void* cache, void* out, const float* sinks,
                                              const int* tiles, int n_tiles, const int* cu_seqlens,
                                              const int* ctx_lens, const int* block_tables, int max_blocks, int nh,
                                              int dk, int dv, int page_size, float scale, int window,
@@ -447,7 +495,7 @@ extern "C" int rlis_attention_latent_prefill(const float* qa, const void* cache,
     if (n_tiles <= 0) return 0;
     if (!rlis_attention_latent_mma_takes(dk, dv) || n_tiles > 65535 || nh <= 0) return RLIS_ERR_UNSUPPORTED;
     LatentArgs a = {qa, (const bf16*)cache, (bf16*)out, sinks, tiles, cu_seqlens, ctx_lens, block_tables, nullptr,
-                    nullptr, nullptr, max_blocks, nh, dk, page_size, window, 1, 0, scale};
+                    nullptr, nullptr, max_blocks, nh, dk, page_size, window, 1, 0, scale, q_bf16};
     dim3 grid(nh, n_tiles);
     switch (dv) {
         case 64: return launch_latent<64, true>(a, grid, dv, stream);
@@ -459,18 +507,18 @@ extern "C" int rlis_attention_latent_prefill(const float* qa, const void* cache,
 
 // pieces > 1: `scratch` holds n_dec * ceil(nh / 16) * pieces * 16 * (dv + 2) floats and the context
 // is cut into pieces of `piece_keys` keys (a multiple of 64).
-extern "C" int rlis_attention_latent_decode(const float* qa, const void* cache, void* out, const float* sinks,
+extern "C" int rlis_attention_latent_decode(const void* qa, int q_bf16, const void* cache, void* out, const float* sinks,
                                             float* scratch, const int* dec_rows, const int* dec_seqs,
                                             const int* ctx_lens, const int* block_tables, int max_blocks, int n_dec,
                                             int nh, int dk, int dv, int page_size, float scale, int window,
                                             int pieces, int piece_keys, cudaStream_t stream) {
     if (n_dec <= 0) return 0;
-    if (!rlis_attention_latent_mma_takes(dk, dv) || n_dec > 65535 || nh <= 0 || pieces < 1 || pieces > 65535 ||
-        (pieces > 1 && (scratch == nullptr || piece_keys <= 0 || piece_keys % LF_BN)))
+    if (!rlis_attention_latent_mma_takes(dk, dv) || n_dec > 65535 || nh <= 0 || pieces < 1 || pieces > 4096 ||
+        (pieces > 1 && (scratch == nullptr || piece_keys <= 0 || piece_keys % LF_BN_MAX)))
         return RLIS_ERR_UNSUPPORTED;
     if (pieces == 1) piece_keys = 0x40000000;
     LatentArgs a = {qa, (const bf16*)cache, (bf16*)out, sinks, nullptr, nullptr, ctx_lens, block_tables, dec_rows,
-                    dec_seqs, scratch, max_blocks, nh, dk, page_size, window, pieces, piece_keys, scale};
+                    dec_seqs, scratch, max_blocks, nh, dk, page_size, window, pieces, piece_keys, scale, q_bf16};
     const int head_tiles = (nh + 15) / 16;
     dim3 grid(head_tiles, n_dec, pieces);
     int rc;
@@ -483,10 +531,10 @@ extern "C" int rlis_attention_latent_decode(const float* qa, const void* cache, 
     if (rc != 0 || pieces == 1) return rc;
     dim3 mgrid(nh, n_dec);
     switch (dv) {
-        case 64: rlis_launch(latent_merge_kernel<64>, mgrid, 64, 0, stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
-        case 128: rlis_launch(latent_merge_kernel<128>, mgrid, 128, 0, stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
-        case 256: rlis_launch(latent_merge_kernel<256>, mgrid, 128, 0, stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
-        default: rlis_launch(latent_merge_kernel<512>, mgrid, 128, 0, stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
+        case 64: rlis_launch(latent_merge_kernel<64>, mgrid, 64, (size_t)2 * pieces * sizeof(float), stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
+        case 128: rlis_launch(latent_merge_kernel<128>, mgrid, 128, (size_t)2 * pieces * sizeof(float), stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
+        case 256: rlis_launch(latent_merge_kernel<256>, mgrid, 128, (size_t)2 * pieces * sizeof(float), stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
+        default: rlis_launch(latent_merge_kernel<512>, mgrid, 128, (size_t)2 * pieces * sizeof(float), stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
     }
     return RLIS_LAUNCH_CHECK();
 }

@@ -306,15 +306,18 @@ def latent_kv_store(z: torch.Tensor, weight: torch.Tensor, eps: float, inv_freq:
 def latent_q_rope(q: torch.Tensor, qa: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int, magnitude: float,
                   positions: torch.Tensor, n_heads: int, d_plain: int, rot: int, rank: int) -> torch.Tensor:
     """qa[t, h, rank:] = the rotated part q[t, h, d_plain:] after rotation, in float32.  q [T, nh (d_plain
-    + rot)] in the activation type; qa float32 [T, nh (rank + rot)]."""
+    + rot)] in the activation type; qa [T, nh (rank + rot)] float32, or bfloat16 for the tensor-core
+    attention kernels."""
     T = q.shape[0]
     _req(q, "q", None, (T, n_heads * (d_plain + rot)))
-    _req(qa, "qa", torch.float32, (T, n_heads * (rank + rot)))
+    _req(qa, "qa", None, (T, n_heads * (rank + rot)))
+    if qa.dtype not in (torch.float32, torch.bfloat16) or (qa.dtype == torch.bfloat16 and q.dtype != torch.bfloat16):
+        raise KernelError(f"latent_q_rope: qa of {qa.dtype} for q of {q.dtype} is not taken")
     _req(inv_freq, "inv_freq", torch.float32, (rot_dims // 2,))
     _req(positions, "positions", torch.int32, (T,))
     check(lib().rlis_latent_q_rope(q.data_ptr(), qa.data_ptr(), inv_freq.data_ptr(), positions.data_ptr(), T,
                                    n_heads, d_plain, rot, int(rot_dims), rank, float(magnitude), _code(q.dtype),
-                                   _stream()), "latent_q_rope")
+                                   1 if qa.dtype == torch.bfloat16 else 0, _stream()), "latent_q_rope")
     _count("latent_q_rope")
     return qa
 
@@ -335,10 +338,10 @@ def _latent_mma_sizes(dk: int, rank: int) -> bool:
 @functools.lru_cache(maxsize=4096)
 def _latent_decode_pieces(n_decode: int, head_tiles: int, max_ctx: int, sms: int) -> tuple:
     """(pieces, keys a piece) for decode attention over latent rows: a CTA takes 16 heads of one
-    token and holds an SM by its shared memory, so the context is cut until the CTAs about fill the
-    SMs, in pieces that are multiples of 64 keys and at least 256 long."""
+    token and two fit an SM's shared memory, so the context is cut until the CTAs about fill the SMs
+    twice, in pieces that are multiples of 64 keys and at least 128 long."""
     ctas = max(1, n_decode * head_tiles)
-    want = max(1, min(sms // ctas, max_ctx // 256))
+    want = max(1, min(2 * sms // ctas, max_ctx // 128))
     keys = -(-max_ctx // want)
     keys = -(-keys // 64) * 64
     return max(1, -(-max_ctx // keys)), keys
@@ -348,30 +351,48 @@ def latent_decode_pieces(n_decode: int, n_heads: int, max_ctx: int) -> tuple:
     return _latent_decode_pieces(int(n_decode), (int(n_heads) + 15) // 16, max(1, int(max_ctx)), num_sms())
 
 
+def _latent_step_takes_mma(step, dtype, dk: int, rank: int) -> bool:
+    """Whether every token of the step goes to the tensor-core kernels: the sizes fit, and the step's
+    prompt portions (if any) are listed in tiles."""
+    n_dec, n_tiles = getattr(step, "n_decode", 0), getattr(step, "n_prefill_tiles", 0)
+    return bool(latent_attention_takes_mma(dtype, dk, rank) and (n_dec or n_tiles)
+                and (n_tiles or not getattr(step, "n_prefill_tokens", 0)))
+
+
+def latent_attention_queries_dtype(step, dtype, dk: int, rank: int):
+    """The element type `attention_latent` wants its folded queries in for this step: bfloat16 when all
+    of it goes to the tensor-core kernels (they copy the queries into shared memory as they are),
+    float32 otherwise."""
+    return torch.bfloat16 if _latent_step_takes_mma(step, dtype, dk, rank) else torch.float32
+
+
 def attention_latent(qa: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, step, group: int, n_heads: int,
                      rank: int, page_size: int, scale: float, sinks: torch.Tensor | None = None,
                      window: int = 0) -> torch.Tensor:
     """Causal attention of every token of the step over its request's cached latent rows, which all
     heads share: score = scale * qa[t, h] . row, out[t, h] = sum of softmax weights times row[:rank].
     `sinks` float32 [nh]: exp(sink_h) joins the denominator of head h and nothing else.  qa float32
-    [T, nh dk]; cache [pages, 1, page_size, dk]; out [T, nh rank] in the cache's type.
+    [T, nh dk] (bfloat16 is taken too when the whole step goes to the tensor-core kernels, see
+    `latent_attention_queries_dtype`); cache [pages, 1, page_size, dk]; out [T, nh rank] in the cache's type.
 
     bfloat16 with sizes the tensor-core kernels take: single decoded tokens go to the split decode
     kernel, portions of prompts (the step's tile list) to the flash kernel.  Everything else, and all
     of float32, to the kernel that takes one warp a (token, head)."""
     T = qa.shape[0]
     dk = cache.shape[-1]
-    _req(qa, "qa", torch.float32, (T, n_heads * dk))
+    _req(qa, "qa", None, (T, n_heads * dk))
     _req(cache, "cache", None, (None, 1, page_size, dk))
     _req(out, "out", cache.dtype, (T, n_heads * rank))
     if sinks is not None:
         _req(sinks, "sinks", torch.float32, (n_heads,))
+    if qa.dtype != latent_attention_queries_dtype(step, cache.dtype, dk, rank) and qa.dtype != torch.float32:
+        raise KernelError(f"attention_latent: queries of {qa.dtype} where this step takes float32")
+    q16 = 1 if qa.dtype == torch.bfloat16 else 0
     tables = step.block_tables[group]
     sink_ptr = sinks.data_ptr() if sinks is not None else None
     n_dec = getattr(step, "n_decode", 0)
     n_tiles = getattr(step, "n_prefill_tiles", 0)
-    if latent_attention_takes_mma(cache.dtype, dk, rank) and (n_dec or n_tiles) and \
-            (n_tiles or not getattr(step, "n_prefill_tokens", 0)):
+    if _latent_step_takes_mma(step, cache.dtype, dk, rank):
         if n_dec:
             pieces, keys = latent_decode_pieces(n_dec, n_heads, step.max_decode_ctx)
             scratch = None
@@ -379,7 +400,7 @@ def attention_latent(qa: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, s
                 scratch = step.buffer("latent_partial", (n_dec * ((n_heads + 15) // 16) * pieces * 16 * (rank + 2),),
                                       torch.float32)
             check(lib().rlis_attention_latent_decode(
-                qa.data_ptr(), cache.data_ptr(), out.data_ptr(), sink_ptr,
+                qa.data_ptr(), q16, cache.data_ptr(), out.data_ptr(), sink_ptr,
                 scratch.data_ptr() if scratch is not None else None, step.dec_rows.data_ptr(),
                 step.dec_seqs.data_ptr(), step.ctx_lens.data_ptr(), tables.data_ptr(), tables.shape[1], n_dec,
                 n_heads, dk, rank, page_size, float(scale), int(window), pieces, keys, _stream()),
@@ -387,7 +408,7 @@ def attention_latent(qa: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, s
             _count("attention_latent.decode.mma" + (".split" if pieces > 1 else ""))
         if n_tiles:
             check(lib().rlis_attention_latent_prefill(
-                qa.data_ptr(), cache.data_ptr(), out.data_ptr(), sink_ptr, step.prefill_tiles.data_ptr(), n_tiles,
+                qa.data_ptr(), q16, cache.data_ptr(), out.data_ptr(), sink_ptr, step.prefill_tiles.data_ptr(), n_tiles,
                 step.cu_seqlens.data_ptr(), step.ctx_lens.data_ptr(), tables.data_ptr(), tables.shape[1], n_heads,
                 dk, rank, page_size, float(scale), int(window), _stream()), "attention_latent_prefill")
             _count("attention_latent.prefill.mma")

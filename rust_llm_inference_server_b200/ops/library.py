@@ -33,11 +33,11 @@ SIGNATURES = {
     "rlis_act_norm": [P, LL, I, P, P, LL, P, LL, I, I, F, I, P],
     "rlis_bias_act": [P, P, P, LL, I, I, I, P],
     "rlis_latent_kv_store": [P, LL, P, P, P, P, P, I, I, I, I, F, F, I, P],
-    "rlis_latent_q_rope": [P, P, P, P, I, I, I, I, I, I, F, I, P],
+    "rlis_latent_q_rope": [P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "rlis_attention_latent": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "rlis_attention_latent_mma_takes": [I, I],
-    "rlis_attention_latent_prefill": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
-    "rlis_attention_latent_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
+    "rlis_attention_latent_prefill": [P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
+    "rlis_attention_latent_decode": [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "rlis_lightning_scan": [P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, I, P, I, P],
     "rlis_rope_cache": [P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "rlis_attention_generic": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],

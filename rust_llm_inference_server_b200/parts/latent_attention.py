@@ -100,7 +100,9 @@ class LatentAttention(Mixer):
                               step.buffer("latent_cq", (T, s.q_rank), self.dtype))
         with span("q up proj"):
             q = ops.linear(cq, self.w_q_up)
-        qa = step.buffer("latent_qa", (T, H * dk), torch.float32)
+        # float32, or bfloat16 when the whole step goes to the tensor-core attention kernels
+        qa_dtype = ops.latent_attention_queries_dtype(step, self.dtype, dk, s.kv_rank)
+        qa = step.buffer("latent_qa" if qa_dtype == torch.float32 else "latent_qa16", (T, H * dk), qa_dtype)
         with span("q fold + rope"):
             ops.per_head_linear(q.view(T, H, s.dim + s.rot_dim)[:, :, :s.dim], self.w_k_fold,
                                 qa.view(T, H, dk)[:, :, :s.kv_rank])

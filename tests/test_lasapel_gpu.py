@@ -283,6 +283,12 @@ def test_tensor_core_attention_over_latents(H, rank, rot, window, use_sinks):
                          dev(sinks) if use_sinks else None, window)
     assert ops.launches_by_kernel.get("attention_latent.decode.mma.split") and ops.launches_by_kernel.get("attention_latent.prefill.mma")
     np.testing.assert_allclose(out.float().cpu().numpy().reshape(step.n_tokens, H, rank), want, rtol=0, atol=2e-2)
+    # queries that are bfloat16 already (as the mixer hands them over) are copied as they are
+    assert ops.latent_attention_queries_dtype(step, torch.bfloat16, dk, rank) == torch.bfloat16
+    out.fill_(9.0)
+    ops.attention_latent(dev(qa.reshape(step.n_tokens, -1), torch.bfloat16), cache, out, step, 0, H, rank, page, 0.3,
+                         dev(sinks) if use_sinks else None, window)
+    np.testing.assert_allclose(out.float().cpu().numpy().reshape(step.n_tokens, H, rank), want, rtol=0, atol=2e-2)
     # short contexts alone are not cut into pieces
     short = [(15, 1), (16, 1), (0, 1)]
     step2 = FakeStep(short, tables[[3, 4, 0]])
@@ -441,3 +447,46 @@ def test_greedy_generation_through_the_entry_point(model_root, dtype):
             gap = lg[want[i]] - lg[o.token_ids[i]]
             assert dtype == "bfloat16" and gap < 0.1, f"parted at token {i} with a gap of {gap}"
     assert llm.engine.cache.check_invariants() == "" if hasattr(llm.engine, "cache") else True
+
+
+def test_command_line_serves_the_design(tmp_path):
+    """random-weights, generate and perplexity of the command line with a Lasapel folder."""
+    import json
+    import math
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def rlis(*args):
+        return subprocess.run([sys.executable, os.path.join(root, "bin", "rlis"), *args], capture_output=True,
+                              text=True, timeout=600)
+
+    cfg_file = tmp_path / "c.json"
+    cfg_file.write_text(json.dumps(U.CONFIGS["X"]))
+    d = str(tmp_path / "m")
+    r = rlis("random-weights", "--config", str(cfg_file), "--seed", "21", "--out", d)
+    assert r.returncode == 0, r.stderr[-2000:]
+    cfg, w = U.read_config(d), U.plain_weights(d)
+    assert cfg["architecture"] == "Lasapel" and set(w) == set(U.tensor_shapes(cfg))
+    prompt = [5, 9, 200, 31, 7]
+    r = rlis("generate", "--model", d, "--dtype", "f32", "--prompt-ids", ",".join(map(str, prompt)),
+             "--max-tokens", "8", "--max-seq-len", "64", "--kv-cache-gb", "0.001", "--block-size", "8",
+             "--max-num-seqs", "2")
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [int(t) for t in r.stdout.split()] == plain_greedy(cfg, w, prompt, 8)
+    toks = np.random.default_rng(0).integers(0, cfg["vocab"], size=2 * 32 + 5).tolist()
+    f = tmp_path / "toks.txt"
+    f.write_text(" ".join(map(str, toks)))
+    r = rlis("perplexity", "--model", d, "--dtype", "f32", "--token-file", str(f), "--ctx", "32")
+    assert r.returncode == 0, r.stderr[-2000:]
+    rep = json.loads(r.stdout.strip().splitlines()[-1])
+    nll = []
+    for wdw in range(2):
+        chunk = toks[wdw * 32:(wdw + 1) * 32]
+        chunk[0] = toks[0]
+        lg = P.forward(cfg, w, chunk)
+        lp = lg - np.log(np.exp(lg - lg.max(-1, keepdims=True)).sum(-1, keepdims=True)) - lg.max(-1, keepdims=True)
+        nll += [-float(lp[i, chunk[i + 1]]) for i in range(16, 31)]
+    assert rep["windows"] == 2 and abs(rep["mean_nll"] - np.mean(nll)) < 1e-4
+    assert abs(rep["ppl"] - math.exp(np.mean(nll))) < 1e-2
