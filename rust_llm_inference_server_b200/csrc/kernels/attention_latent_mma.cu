@@ -420,6 +420,246 @@ __global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const
     pdl_trigger();
 }
 
+// Two 8x8 b16 matrices; lanes 0..15 supply the row addresses (the others' are ignored but must be valid).
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(smem_u32(smem_row)));
+}
+
+// Decode: 16 heads of one token and one piece of its context a CTA of four warps; stages of 32 keys.
+// Warp w forms the scores of keys 8 w .. 8 w + 7 of a stage (all 16 heads), the four exchange row maxima
+// and the rounded weights through shared memory, and warp w sums the values' columns w DV/4 .. (w+1) DV/4
+// over all 32 keys.  Every warp keeps the same running (max, sum); nothing is merged at the end.
+template <int DV>
+__global__ __launch_bounds__(128) void latent_decode_kernel(const LatentArgs a) {
+    pdl_wait();
+    constexpr int BN = 32, NO = DV / 32, PS = BN + 8;   // keys a stage; output tiles a warp; row pitch of the weights
+    const int dk = a.dk, stride = dk + 8, ksteps = dk / 16, cpr = dk / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);              // [16][stride]
+    bf16* kbuf = qs + 16 * stride;                             // [2][32][stride]
+    bf16* pbuf = kbuf + 2 * BN * stride;                       // [16][PS] weights of a stage, bfloat16
+    float* mxw = reinterpret_cast<float*>(pbuf + 16 * PS);     // [4 warps][16 rows] maxima
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, c = lane & 3;
+    const int nh = a.nh;
+    const int di = blockIdx.y;
+    const int b = a.dec_seqs[di];
+    const int q_row0 = a.dec_rows[di];
+    const int head0 = blockIdx.x * 16;
+    const int pos = a.ctx_lens[b] - 1;
+    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int k_lo = max(lo, (int)blockIdx.z * a.piece_keys);
+    const int k_hi = min(pos + 1, (int)(blockIdx.z + 1) * a.piece_keys);
+    const int* table = a.block_tables + (size_t)b * a.max_blocks;
+    const int page_size = a.page_size;
+
+    if (a.q_bf16) {
+        const bf16* qsrc = reinterpret_cast<const bf16*>(a.qa);
+        for (int idx = threadIdx.x; idx < 16 * cpr; idx += 128) {
+            const int r = idx / cpr, c16 = idx - r * cpr;
+            const bool valid = head0 + r < nh;
+            cp_async16(qs + r * stride + c16 * 8, qsrc + ((size_t)q_row0 * nh + head0 + (valid ? r : 0)) * dk + c16 * 8, valid);
+        }
+    } else {
+        const float* qsrc = reinterpret_cast<const float*>(a.qa);
+        for (int idx = threadIdx.x; idx < 16 * (dk / 2); idx += 128) {
+            const int r = idx / (dk / 2), j = (idx - r * (dk / 2)) * 2;
+            float2 v = make_float2(0.f, 0.f);
+            if (head0 + r < nh) v = *reinterpret_cast<const float2*>(qsrc + ((size_t)q_row0 * nh + head0 + r) * dk + j);
+            *reinterpret_cast<uint32_t*>(qs + r * stride + j) = pack_bf16(v.x, v.y);
+        }
+    }
+    const int kt0 = k_lo / BN, kt1 = k_hi > k_lo ? (k_hi + BN - 1) / BN : kt0;
+    auto issue = [&](int kt, int stage) {      // a warp copies 8 keys' rows, in runs of 512 contiguous bytes
+        const int key0 = kt * BN + warp * 8;
+        long long my_off = -1;
+        if (lane < 8) {
+            const int key = key0 + lane;
+            if (key < k_hi && key >= k_lo) {
+                const int pi = key / page_size;
+                my_off = ((long long)table[pi] * page_size + (key - pi * page_size)) * dk;
+            }
+        }
+        bf16* dst0 = kbuf + ((size_t)stage * BN + warp * 8) * stride;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const long long off = __shfl_sync(0xffffffffu, my_off, k);
+            const bool valid = off >= 0;
+            const bf16* src = a.cache + (valid ? off : 0);
+            for (int c16 = lane; c16 < cpr; c16 += 32) cp_async16(dst0 + k * stride + c16 * 8, src + c16 * 8, valid);
+        }
+        cp_async_commit();
+    };
+
+    const int h0 = head0 + g, h1 = h0 + 8;
+    const bool rv0 = h0 < nh, rv1 = h1 < nh;
+    // the sink is one more key with a score of its own and no value; it belongs to the first piece
+    const bool has_sink = a.sinks != nullptr && blockIdx.z == 0;
+    float m_run[2], l_run[2];
+    m_run[0] = has_sink && rv0 ? a.sinks[h0] * LOG2E : -INFINITY;
+    m_run[1] = has_sink && rv1 ? a.sinks[h1] * LOG2E : -INFINITY;
+    l_run[0] = has_sink && rv0 ? 1.f : 0.f;
+    l_run[1] = has_sink && rv1 ? 1.f : 0.f;
+    float oacc[NO][4];
+#pragma unroll
+    for (int n = 0; n < NO; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[n][e] = 0.f;
+    const float scale_log2 = a.scale * LOG2E;
+    const int col0 = warp * (DV / 4);
+
+    if (kt0 < kt1) issue(kt0, 0); else { cp_async_commit(); }
+    int stage = 0;
+    for (int kt = kt0; kt < kt1; ++kt) {
+        cp_async_wait<0>();
+        __syncthreads();                       // this stage has landed, and everybody is done with the other one
+        if (kt + 1 < kt1) issue(kt + 1, stage ^ 1);
+        const bf16* kst = kbuf + (size_t)stage * BN * stride;
+
+        // scores of this warp's 8 keys, two chains of products
+        float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+        const bf16* qrow = qs + (((lane >> 3) & 1) * 8 + (lane & 7)) * stride + (lane >> 4) * 8;
+        const bf16* krow = kst + (warp * 8 + (lane & 7)) * stride + ((lane >> 3) & 1) * 8;
+        int ks = 0;
+        for (; ks + 1 < ksteps; ks += 2) {
+            uint32_t qa0[4], qa1[4], b0, b1, b2, b3;
+            ldmatrix_x4(qa0, qrow + ks * 16);
+            ldmatrix_x2(b0, b1, krow + ks * 16);
+            ldmatrix_x4(qa1, qrow + ks * 16 + 16);
+            ldmatrix_x2(b2, b3, krow + ks * 16 + 16);
+            mma_bf16_16816(sa, qa0, b0, b1);
+            mma_bf16_16816(sb, qa1, b2, b3);
+        }
+        if (ks < ksteps) {
+            uint32_t qa0[4], b0, b1;
+            ldmatrix_x4(qa0, qrow + ks * 16);
+            ldmatrix_x2(b0, b1, krow + ks * 16);
+            mma_bf16_16816(sa, qa0, b0, b1);
+        }
+        float s[4];
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int key = kt * BN + warp * 8 + 2 * c + e;
+            const bool seen = key <= pos && key >= k_lo && key < k_hi;
+            s[e] = rv0 && seen ? (sa[e] + sb[e]) * scale_log2 : -INFINITY;
+            s[2 + e] = rv1 && seen ? (sa[2 + e] + sb[2 + e]) * scale_log2 : -INFINITY;
+            mx0 = fmaxf(mx0, s[e]);
+            mx1 = fmaxf(mx1, s[2 + e]);
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        if (c == 0) {
+            mxw[warp * 16 + g] = mx0;
+            mxw[warp * 16 + g + 8] = mx1;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            mx0 = fmaxf(mx0, mxw[w * 16 + g]);
+            mx1 = fmaxf(mx1, mxw[w * 16 + g + 8]);
+        }
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float corr0 = exp2f(m_run[0] - ms0), corr1 = exp2f(m_run[1] - ms1);
+        *reinterpret_cast<uint32_t*>(pbuf + g * PS + warp * 8 + 2 * c) = pack_bf16(exp2f(s[0] - ms0), exp2f(s[1] - ms0));
+        *reinterpret_cast<uint32_t*>(pbuf + (g + 8) * PS + warp * 8 + 2 * c) = pack_bf16(exp2f(s[2] - ms1), exp2f(s[3] - ms1));
+        __syncthreads();
+        // all 32 keys' weights as the A operand; the row sums are taken over the rounded weights
+        uint32_t pa[2][4];
+        float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            ldmatrix_x4(pa[kk], pbuf + (((lane >> 3) & 1) * 8 + (lane & 7)) * PS + kk * 16 + (lane >> 4) * 8);
+            const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pa[kk][0]));
+            const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pa[kk][1]));
+            const float2 a2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pa[kk][2]));
+            const float2 a3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pa[kk][3]));
+            ls0 += (a0.x + a0.y) + (a2.x + a2.y);
+            ls1 += (a1.x + a1.y) + (a3.x + a3.y);
+        }
+        ls0 += __shfl_xor_sync(0xffffffffu, ls0, 1);
+        ls0 += __shfl_xor_sync(0xffffffffu, ls0, 2);
+        ls1 += __shfl_xor_sync(0xffffffffu, ls1, 1);
+        ls1 += __shfl_xor_sync(0xffffffffu, ls1, 2);
+        l_run[0] = l_run[0] * corr0 + ls0;
+        l_run[1] = l_run[1] * corr1 + ls1;
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+#pragma unroll
+        for (int n = 0; n < NO; ++n) {
+            oacc[n][0] *= corr0;
+            oacc[n][1] *= corr0;
+            oacc[n][2] *= corr1;
+            oacc[n][3] *= corr1;
+        }
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+            for (int n2 = 0; n2 < NO / 2; ++n2) {
+                uint32_t vb[4];
+                const int mat = lane >> 3;
+                ldmatrix_x4_trans(vb, kst + (kk * 16 + (mat & 1) * 8 + (lane & 7)) * stride + col0 + (n2 * 2 + (mat >> 1)) * 8);
+                mma_bf16_16816(oacc[2 * n2], pa[kk], vb[0], vb[1]);
+                mma_bf16_16816(oacc[2 * n2 + 1], pa[kk], vb[2], vb[3]);
+            }
+        }
+        stage ^= 1;
+    }
+    cp_async_wait<0>();
+
+    if (a.pieces == 1) {
+        const float inv0 = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
+        if (rv0) {
+            bf16* o = a.out + ((size_t)q_row0 * nh + h0) * DV + col0;
+#pragma unroll
+            for (int n = 0; n < NO; ++n)
+                *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(oacc[n][0] * inv0, oacc[n][1] * inv0);
+        }
+        if (rv1) {
+            bf16* o = a.out + ((size_t)q_row0 * nh + h1) * DV + col0;
+#pragma unroll
+            for (int n = 0; n < NO; ++n)
+                *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(oacc[n][2] * inv1, oacc[n][3] * inv1);
+        }
+    } else {
+        float* part = a.scratch + (((size_t)blockIdx.y * gridDim.x + blockIdx.x) * a.pieces + blockIdx.z) * 16 * (DV + 2);
+        float* p0 = part + g * (DV + 2);
+        float* p1 = part + (g + 8) * (DV + 2);
+        if (warp == 0 && c == 0) {
+            p0[DV] = m_run[0]; p0[DV + 1] = l_run[0];
+            p1[DV] = m_run[1]; p1[DV + 1] = l_run[1];
+        }
+#pragma unroll
+        for (int n = 0; n < NO; ++n) {
+            const int col = col0 + n * 8 + 2 * c;
+            *reinterpret_cast<float2*>(p0 + col) = make_float2(oacc[n][0], oacc[n][1]);
+            *reinterpret_cast<float2*>(p1 + col) = make_float2(oacc[n][2], oacc[n][3]);
+        }
+    }
+    pdl_trigger();
+}
+
+static size_t latent_decode_smem_bytes(int dk) {
+    return (size_t)(16 + 2 * 32) * (dk + 8) * sizeof(bf16) + (size_t)16 * (32 + 8) * sizeof(bf16) + 4 * 16 * sizeof(float);
+}
+
+template <int DV>
+int launch_latent_decode(const LatentArgs& a, dim3 grid, cudaStream_t stream) {
+    const size_t smem = latent_decode_smem_bytes(a.dk);
+    if (smem > 227 * 1024) return RLIS_ERR_UNSUPPORTED;
+    static size_t allowed = 0;
+    if (smem > allowed) {
+        cudaFuncSetAttribute(latent_decode_kernel<DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        allowed = smem;
+    }
+    rlis_launch(latent_decode_kernel<DV>, grid, 128, smem, stream, a);
+    return RLIS_LAUNCH_CHECK();
+}
+
 // One CTA a (decoded token, head): folds the pieces' (max, sum, output) into the output row.  The
 // pieces' weights exp2(max_p - max) are worked out once, by one thread a piece.
 template <int DV>
@@ -451,11 +691,16 @@ __global__ void latent_merge_kernel(const float* __restrict__ scratch, bf16* __r
     l = block_sum(l, red);                         // (its barriers also publish the weights)
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     bf16* o = out + ((size_t)dec_rows[di] * nh + h) * DV;
-    for (int col = threadIdx.x; col < DV; col += blockDim.x) {
-        float acc = 0.f;
+    // two columns a thread at a time (rows of DV + 2 floats are 8-byte aligned), eight pieces' loads in flight
+    for (int col = threadIdx.x * 2; col < DV; col += blockDim.x * 2) {
+        float a0 = 0.f, a1 = 0.f;
 #pragma unroll 8
-        for (int p = 0; p < pieces; ++p) acc = fmaf(part[p * piece_stride + col], wts[p], acc);
-        o[col] = __float2bfloat16_rn(acc * inv);
+        for (int p = 0; p < pieces; ++p) {
+            const float2 v = *reinterpret_cast<const float2*>(part + p * piece_stride + col);
+            a0 = fmaf(v.x, wts[p], a0);
+            a1 = fmaf(v.y, wts[p], a1);
+        }
+        *reinterpret_cast<uint32_t*>(o + col) = pack_bf16(a0 * inv, a1 * inv);
     }
 }
 
@@ -523,18 +768,18 @@ extern "C" int rlis_attention_latent_decode(const void* qa, int q_bf16, const vo
     dim3 grid(head_tiles, n_dec, pieces);
     int rc;
     switch (dv) {
-        case 64: rc = launch_latent<64, false>(a, grid, dv, stream); break;
-        case 128: rc = launch_latent<128, false>(a, grid, dv, stream); break;
-        case 256: rc = launch_latent<256, false>(a, grid, dv, stream); break;
-        default: rc = launch_latent<512, false>(a, grid, dv, stream); break;
+        case 64: rc = launch_latent_decode<64>(a, grid, stream); break;
+        case 128: rc = launch_latent_decode<128>(a, grid, stream); break;
+        case 256: rc = launch_latent_decode<256>(a, grid, stream); break;
+        default: rc = launch_latent_decode<512>(a, grid, stream); break;
     }
     if (rc != 0 || pieces == 1) return rc;
     dim3 mgrid(nh, n_dec);
     switch (dv) {
-        case 64: rlis_launch(latent_merge_kernel<64>, mgrid, 64, (size_t)2 * pieces * sizeof(float), stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
-        case 128: rlis_launch(latent_merge_kernel<128>, mgrid, 128, (size_t)2 * pieces * sizeof(float), stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
+        case 64: rlis_launch(latent_merge_kernel<64>, mgrid, 32, (size_t)2 * pieces * sizeof(float), stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
+        case 128: rlis_launch(latent_merge_kernel<128>, mgrid, 64, (size_t)2 * pieces * sizeof(float), stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
         case 256: rlis_launch(latent_merge_kernel<256>, mgrid, 128, (size_t)2 * pieces * sizeof(float), stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
-        default: rlis_launch(latent_merge_kernel<512>, mgrid, 128, (size_t)2 * pieces * sizeof(float), stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
+        default: rlis_launch(latent_merge_kernel<512>, mgrid, 256, (size_t)2 * pieces * sizeof(float), stream, (const float*)scratch, (bf16*)out, dec_rows, nh, head_tiles, pieces); break;
     }
     return RLIS_LAUNCH_CHECK();
 }

@@ -322,6 +322,7 @@ def latent_q_rope(q: torch.Tensor, qa: torch.Tensor, inv_freq: torch.Tensor, rot
     return qa
 
 
+LATENT_DECODE_CTAS_PER_SM = 2   # debug switch "latent_ctas_per_sm": how full decode attention over latents fills the SMs
 LATENT_MMA = True          # debug switch "latent_mma": 0 takes the one-warp-a-row kernel for every size
 
 
@@ -341,7 +342,7 @@ def _latent_decode_pieces(n_decode: int, head_tiles: int, max_ctx: int, sms: int
     token and two fit an SM's shared memory, so the context is cut until the CTAs about fill the SMs
     twice, in pieces that are multiples of 64 keys and at least 128 long."""
     ctas = max(1, n_decode * head_tiles)
-    want = max(1, min(2 * sms // ctas, max_ctx // 128))
+    want = max(1, min(LATENT_DECODE_CTAS_PER_SM * sms // ctas, max_ctx // 128))
     keys = -(-max_ctx // want)
     keys = -(-keys // 64) * 64
     return max(1, -(-max_ctx // keys)), keys
@@ -836,13 +837,19 @@ def _set_flag(name):
     return setter
 
 
+def _set_latent_ctas(value):
+    global LATENT_DECODE_CTAS_PER_SM
+    LATENT_DECODE_CTAS_PER_SM = max(1, int(value))
+    _latent_decode_pieces.cache_clear()
+
+
 def _set_stream_rows(value):
     global STREAM_GEMM_ROWS
     STREAM_GEMM_ROWS = max(DECODE_GEMM_ROWS, min(int(value), STREAM_MAX_ROWS))
 
 
 library.PYTHON_SWITCHES.update(fuse_norms=_set_flag("FUSE_NORMS"), prefill_tcgen05=_set_flag("PREFILL_TCGEN05"),
-                               latent_mma=_set_flag("LATENT_MMA"),
+                               latent_mma=_set_flag("LATENT_MMA"), latent_ctas_per_sm=_set_latent_ctas,
                                stream_rows=_set_stream_rows)
 
 
