@@ -78,6 +78,16 @@ def peaks() -> tuple:
     return dict(FALLBACK_PEAKS), "fallback"
 
 
+def _peak_extra(key: str, default: float) -> float:
+    """A number of MEASURED_PEAKS.json beyond the three peaks (the SMs' maximum clock)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            v = json.load(f).get(key)
+        return float(v) if isinstance(v, (int, float)) else default
+    except (OSError, ValueError):
+        return default
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
 
@@ -464,13 +474,112 @@ def prefill_run(llm, tokens: int, iters: int, warmup: int, torch, np) -> float:
     return statistics.median(times[warmup:])
 
 
+class _KernelStep:
+    """The device arrays of a step that the mixers' kernels read, for requests given as (tokens cached
+    before, tokens now); every request gets pages of its own in shuffled order."""
+
+    def __init__(self, reqs, page, torch, np, tile=64):
+        dev = lambda x: torch.as_tensor(np.asarray(x), dtype=torch.int32).cuda().contiguous()
+        lens = [n for _, n in reqs]
+        cu = np.cumsum([0] + lens)
+        pages = [-(-(s + n) // page) for s, n in reqs]
+        perm = np.random.default_rng(0).permutation(sum(pages))
+        tables = np.full((len(reqs), max(pages)), -1, dtype=np.int32)
+        k = 0
+        for b, m in enumerate(pages):
+            tables[b, :m] = perm[k:k + m]
+            k += m
+        self.n_pages, self.n_tokens, self.n_seqs = int(sum(pages)), int(cu[-1]), len(reqs)
+        self.block_tables = [dev(tables)]
+        self.positions = dev(np.concatenate([np.arange(s, s + n) for s, n in reqs]))
+        self.seq_of_token = dev(np.concatenate([np.full(n, b) for b, (_, n) in enumerate(reqs)]))
+        self.cu_seqlens, self.ctx_lens = dev(cu), dev([s + n for s, n in reqs])
+        self.state_slots = dev(list(range(len(reqs))))
+        dec = [b for b, (_, n) in enumerate(reqs) if n == 1]
+        self.n_decode, self.dec_seqs, self.dec_rows = len(dec), dev(dec), dev([cu[b] for b in dec])
+        self.max_decode_ctx = max([reqs[b][0] + 1 for b in dec], default=0)
+        self.max_ctx_len = max(s + n for s, n in reqs)
+        tiles = [(b, t0) for b, (_, n) in enumerate(reqs) if n > 1 for t0 in range(0, n, tile)]
+        self.n_prefill_tiles, self.n_prefill_tokens = len(tiles), sum(n for _, n in reqs if n > 1)
+        self.prefill_tiles = dev(np.asarray(tiles).reshape(-1, 2)) if tiles else None
+        self._bufs, self._torch = {}, torch
+
+    def buffer(self, name, shape, dtype):
+        key = (name, tuple(shape), dtype)
+        if key not in self._bufs:
+            self._bufs[key] = self._torch.empty(tuple(shape), dtype=dtype, device="cuda")
+        return self._bufs[key]
+
+
+def _graph_time_us(fn, torch, iters: int = 20) -> float:
+    """Device time of one call of `fn` replayed from a CUDA graph (no host time between its kernels),
+    L2 flushed before every replay."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total = 0.0
+    for _ in range(iters):
+        flush.zero_()
+        s.record()
+        g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters * 1e3
+
+
+def mixer_kernel_rooflines(width: int, B: int, ctx: int, T: int, pk: dict, torch, np) -> dict:
+    """The mixers' kernels alone at the sizes of `lasapel_config(width)` and `llama_config_like(width)`:
+    {name: {"us", "ideal_us", "frac"}}.  Ideal: bytes that must move over the measured copy bandwidth, or
+    FLOPs over the measured bfloat16 GEMM rate (attention over prompts), or float32 FMAs over the FFMA
+    rate of the SMs at their maximum clock (the recurrence over prompts, which is float32 by design)."""
+    from rust_llm_inference_server_b200 import ops
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    ffma = sms * 128 * 2 * pk.get("sm_max_mhz", 1965.0) * 1e6
+    page, H, rank, rot, d = 16, width // 128, 512, 64, 128
+    dk = rank + rot
+    nh, nkv, hd = width // 64, width // 256, 64
+    bf, out = torch.bfloat16, {}
+    rnd = lambda *shape: torch.randn(*shape, device="cuda") * 0.3
+
+    def row(name, us, ideal_s):
+        out[name] = {"us": round(us, 1), "ideal_us": round(ideal_s * 1e6, 1), "frac": round(ideal_s * 1e6 / us, 3)}
+
+    for kind, reqs in (("decode", [(ctx - 1, 1)] * B), ("prefill", [(0, T)])):
+        st = _KernelStep(reqs, page, torch, np)
+        n, keys = st.n_tokens, (B * ctx if kind == "decode" else T * (T + 1) // 2)
+        cache, qa = rnd(st.n_pages, 1, page, dk).to(bf), rnd(n, H * dk).to(bf)
+        o, sinks = torch.empty(n, H * rank, dtype=bf, device="cuda"), torch.zeros(H, device="cuda")
+        us = _graph_time_us(lambda: ops.attention_latent(qa, cache, o, st, 0, H, rank, page, 0.07, sinks, 0), torch)
+        row(f"latent_attention_{kind}", us, max(B * ctx * dk * 2 / hbm, 2 * H * keys * (dk + rank) / tf) if kind == "decode"
+            else 2 * H * keys * (dk + rank) / tf)
+        kc, vc, q = rnd(st.n_pages, nkv, page, hd).to(bf), rnd(st.n_pages, nkv, page, hd).to(bf), rnd(n, nh * hd).to(bf)
+        o2 = torch.empty_like(q)
+        us = _graph_time_us(lambda: ops.attention(q, kc, vc, o2, st, 0, nh, nkv, hd, page, 0.125, 0), torch)
+        row(f"gqa_attention_{kind}", us, B * ctx * nkv * hd * 2 * 2 / hbm if kind == "decode" else 2 * nh * keys * 2 * hd / tf)
+        proj = rnd(n, 2 * H * d + 2 * H * d).to(bf)
+        state, decay = torch.zeros(len(reqs), H, d, d, device="cuda"), torch.full((H,), 0.97, device="cuda")
+        o3 = torch.empty(n, H * d, device="cuda")
+        us = _graph_time_us(lambda: ops.lightning_scan(proj, 0, H * d, 2 * H * d, o3, state, decay, st, H, d, d), torch)
+        row(f"recurrence_{kind}", us, B * H * d * d * 4 * 2 / hbm if kind == "decode" else 2 * 2 * T * H * d * d / ffma)
+    return out
+
+
 def workload_lasapel(args, torch, np) -> dict:
     """Prefill (one 2,048-token prompt) and decode (batch 8, context 4,096) of four Lasapel layers
     at two widths beside four Llama layers of the same width, random bfloat16 weights; then the
-    stages of one step by CUDA-event spans, with the mixers' kernels against their rooflines."""
+    stages of one step by CUDA-event spans (eager launches: host time between kernels is in them), and
+    the mixers' kernels alone, replayed from CUDA graphs, against their rooflines."""
     from rust_llm_inference_server_b200 import LLM
     from rust_llm_inference_server_b200.ops import profile
     pk, pk_src = peaks()
+    pk["sm_max_mhz"] = _peak_extra("sm_max_mhz", 1965.0)
     B, ctx, page, T = args.batch, args.context, 16, PREFILL_TOKENS
     steps = min(args.steps, 64)
     out = {"workload": "lasapel", "metric": "prefill and decode tokens/s of four layers, Lasapel beside Llama at equal width",
@@ -503,28 +612,7 @@ def workload_lasapel(args, torch, np) -> dict:
                          "prefill_stage_us": pre_stages, "decode_stage_us": dec_stages}
             del llm
             torch.cuda.empty_cache()
-        H = width // 128
-        la, ll = row["lasapel"], row["llama"]
-        hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
-        mean_ctx = ctx - 4
-
-        def frac(ideal_s, stage_us, calls):
-            return round(ideal_s / (stage_us / calls * 1e-6), 4) if stage_us else None
-
-        # per launch: latent attention reads one row of 576 a key for all heads; grouped-query attention a key and a
-        # value of 64 for every key head; the recurrence reads and writes its float32 state
-        row["rooflines"] = {
-            "latent_attention_decode": frac(max(B * mean_ctx * 576 * 2 / hbm, 2 * B * H * mean_ctx * (576 + 512) / tf),
-                                            la["decode_stage_us"].get("attention"), 2),
-            "gqa_attention_decode": frac(B * mean_ctx * (width // 256) * 64 * 2 * 2 / hbm,
-                                         ll["decode_stage_us"].get("rope + kv write + attention"), 4),
-            "latent_attention_prefill": frac(2 * H * (576 + 512) * T * (T + 1) / 2 / tf, la["prefill_stage_us"].get("attention"), 2),
-            "gqa_attention_prefill": frac(2 * (width // 64) * (64 + 64) * T * (T + 1) / 2 / tf,
-                                          ll["prefill_stage_us"].get("attention"), 4),
-            "recurrence_decode": frac(B * H * 128 * 128 * 4 * 2 / hbm, la["decode_stage_us"].get("decayed recurrence"), 2),
-            "recurrence_prefill_fp32_flops": frac(4 * T * H * 128 * 128 / (pk.get("fp32_tflops", 75.0) * 1e12),
-                                                  la["prefill_stage_us"].get("decayed recurrence"), 2),
-        }
+        row["rooflines"] = mixer_kernel_rooflines(width, B, ctx, T, pk, torch, np)
         out["sizes"][f"width{width}"] = row
     out["clocks"] = clocks.stop()
     head = out["sizes"]["width2048"]["lasapel"]

@@ -4,25 +4,23 @@
 // score = scale * qa . row; values are the first DV entries of the same rows; an optional sink term
 // exp(sink_h) in a head's softmax denominator.
 //
-// A CTA of 8 warps works on 64-key stages brought to shared memory by 16-byte asynchronous copies,
-// double-buffered, rows padded by 8 entries.  A warp holds 16 query rows and HALF of the value
-// columns (DV / 2: its output sums are DV / 4 registers a thread), so two warps share their rows.
-//   prompts: one head x 64 tokens a CTA; warp pair p takes tokens 16 p .. 16 p + 15 and every key.
-//            Each warp of a pair forms the scores of 32 of a stage's keys; the two exchange row
-//            maxima and the rounded weights through shared memory (three barriers of 64 threads).
-//   decode : 16 heads of one token a CTA (two warp pairs, stages of 32 keys: two CTAs fit an SM), and
-//            one piece of its context; warp pair p takes keys 16 p .. 16 p + 15 of every stage, and the
-//            pairs' running (max, sum, output) are merged through shared memory at the end.  Several pieces of a context are merged by
-//            a second small kernel.
+// Keys come to shared memory by 16-byte asynchronous copies, double-buffered, rows padded by 8
+// entries; a warp copies whole rows in runs of 512 contiguous bytes.
+//   prompts: one head x 64 tokens a CTA of 8 warps, stages of 64 keys.  Two warps share 16 tokens:
+//            each holds HALF of the value columns (its output sums are DV / 4 registers a thread) and
+//            forms the scores of 32 of a stage's keys; the two exchange row maxima and the rounded
+//            weights through shared memory (three barriers of 64 threads a stage).
+//   decode : 16 heads of one token and one piece of its context a CTA of 4 warps, stages of 32 keys,
+//            so that two CTAs fit an SM at the widest rows.  Warp w forms the scores of 8 of a stage's
+//            keys and sums a QUARTER of the value columns over all 32; maxima and weights go through
+//            shared memory.  Several pieces of a context are merged by a second small kernel.
 // Queries arrive as bfloat16 (copied asynchronously) or as float32 (rounded once, into shared memory).
 #include "common.cuh"
 #include "mma_utils.cuh"
 #include <math.h>
 
 namespace {
-// prompts: 4 warp pairs (256 threads), 64 keys a stage; decode: 2 pairs (128 threads), 32 keys a stage, so
-// that two CTAs fit an SM's shared memory at the widest rows
-constexpr int LF_BN_MAX = 64;
+constexpr int LF_BN_MAX = 64;             // the longest stage: pieces of a context are multiples of it
 constexpr float LOG2E = 1.4426950408889634f;
 
 // Barrier over the two warps of pair `p` (named barriers 1..4; 0 is __syncthreads).
@@ -45,16 +43,14 @@ struct LatentArgs {
     int q_bf16;
 };
 
-// PREFILL: 64 query rows a CTA, every warp pair sees all 64 keys of a stage (4 score tiles a warp).
-// decode : 16 query rows a CTA, warp pair p sees keys 16 p .. 16 p + 15 of a stage (2 score tiles).
-template <int DV, bool PREFILL>
-__global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const LatentArgs a) {
+// Prompts: 64 query rows (tokens of one head) a CTA, four warp pairs, stages of 64 keys.
+template <int DV>
+__global__ __launch_bounds__(256) void latent_flash_kernel(const LatentArgs a) {
     pdl_wait();
-    constexpr int PAIRS = PREFILL ? 4 : 2;
-    constexpr int LF_THREADS = PAIRS * 64;
-    constexpr int LF_BN = PAIRS * 16;            // keys a stage
-    constexpr int NT = PREFILL ? 4 : 2;          // score tiles (8 keys each) a warp forms a stage
-    constexpr int QR = PREFILL ? 64 : 16;        // query rows a CTA
+    constexpr int LF_THREADS = 256;
+    constexpr int LF_BN = 64;                    // keys a stage
+    constexpr int NT = 4;                        // score tiles (8 keys each) a warp forms a stage
+    constexpr int QR = 64;                       // query rows a CTA
     constexpr int NO = DV / 16;                  // output tiles (8 columns each) a warp owns: half of DV / 8
     const int dk = a.dk, stride = dk + 8, ksteps = dk / 16, cpr = dk / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -66,28 +62,14 @@ __global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const
     const int half = warp & 1, pair = warp >> 1;
     const int nh = a.nh;
 
-    int b, q_row0, n_q_rows, head0, pos_base, k_lo, k_hi;
-    if (PREFILL) {
-        b = a.tiles[2 * blockIdx.y];
-        const int t0 = a.tiles[2 * blockIdx.y + 1];
-        const int q_start = a.cu_seqlens[b], q_len = a.cu_seqlens[b + 1] - q_start;
-        q_row0 = q_start + t0;
-        n_q_rows = min(64, q_len - t0);
-        head0 = blockIdx.x;
-        pos_base = a.ctx_lens[b] - q_len + t0;                 // position of the tile's first token
-        k_hi = pos_base + n_q_rows;                            // exclusive
-        k_lo = a.window > 0 ? max(0, pos_base - a.window + 1) : 0;
-    } else {
-        const int di = blockIdx.y;
-        b = a.dec_seqs[di];
-        q_row0 = a.dec_rows[di];
-        n_q_rows = 1;
-        head0 = blockIdx.x * 16;
-        pos_base = a.ctx_lens[b] - 1;
-        const int lo = a.window > 0 ? max(0, pos_base - a.window + 1) : 0;
-        k_lo = max(lo, blockIdx.z * a.piece_keys);
-        k_hi = min(pos_base + 1, (int)(blockIdx.z + 1) * a.piece_keys);
-    }
+    const int b = a.tiles[2 * blockIdx.y], t0 = a.tiles[2 * blockIdx.y + 1];
+    const int q_start = a.cu_seqlens[b], q_len = a.cu_seqlens[b + 1] - q_start;
+    const int q_row0 = q_start + t0;
+    const int n_q_rows = min(64, q_len - t0);
+    const int head0 = blockIdx.x;
+    const int pos_base = a.ctx_lens[b] - q_len + t0;           // position of the tile's first token
+    const int k_hi = pos_base + n_q_rows;                      // exclusive
+    const int k_lo = a.window > 0 ? max(0, pos_base - a.window + 1) : 0;
     const int* table = a.block_tables + (size_t)b * a.max_blocks;
 
     // queries -> shared memory: bfloat16 ones by 16-byte asynchronous copies (they join the first stage's
@@ -96,9 +78,8 @@ __global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const
         const bf16* qsrc = reinterpret_cast<const bf16*>(a.qa);
         for (int idx = threadIdx.x; idx < QR * cpr; idx += LF_THREADS) {
             const int r = idx / cpr, c16 = idx - r * cpr;
-            const bool valid = PREFILL ? r < n_q_rows : head0 + r < nh;
-            const size_t row = PREFILL ? (size_t)(q_row0 + (valid ? r : 0)) * nh + head0
-                                       : (size_t)q_row0 * nh + head0 + (valid ? r : 0);
+            const bool valid = r < n_q_rows;
+            const size_t row = (size_t)(q_row0 + (valid ? r : 0)) * nh + head0;
             cp_async16(qs + r * stride + c16 * 8, qsrc + row * dk + c16 * 8, valid);
         }
     } else {
@@ -106,11 +87,7 @@ __global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const
         for (int idx = threadIdx.x; idx < QR * (dk / 2); idx += LF_THREADS) {
             const int r = idx / (dk / 2), j = (idx - r * (dk / 2)) * 2;
             float2 v = make_float2(0.f, 0.f);
-            if (PREFILL) {
-                if (r < n_q_rows) v = *reinterpret_cast<const float2*>(qsrc + ((size_t)(q_row0 + r) * nh + head0) * dk + j);
-            } else {
-                if (head0 + r < nh) v = *reinterpret_cast<const float2*>(qsrc + ((size_t)q_row0 * nh + head0 + r) * dk + j);
-            }
+            if (r < n_q_rows) v = *reinterpret_cast<const float2*>(qsrc + ((size_t)(q_row0 + r) * nh + head0) * dk + j);
             *reinterpret_cast<uint32_t*>(qs + r * stride + j) = pack_bf16(v.x, v.y);
         }
     }
@@ -146,30 +123,16 @@ __global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const
     };
 
     // this lane's two rows (g and g + 8 of the warp's 16)
-    const int row_base = PREFILL ? pair * 16 : 0;
-    int pos0, pos1, h0, h1;
-    bool rv0, rv1;
-    if (PREFILL) {
-        rv0 = row_base + g < n_q_rows;
-        rv1 = row_base + g + 8 < n_q_rows;
-        pos0 = pos_base + row_base + g;
-        pos1 = pos0 + 8;
-        h0 = h1 = head0;
-    } else {
-        h0 = head0 + g;
-        h1 = h0 + 8;
-        rv0 = h0 < nh;
-        rv1 = h1 < nh;
-        pos0 = pos1 = pos_base;
-    }
+    const int row_base = pair * 16;
+    const bool rv0 = row_base + g < n_q_rows, rv1 = row_base + g + 8 < n_q_rows;
+    const int pos0 = pos_base + row_base + g, pos1 = pos0 + 8;
     const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
     const int lo1 = a.window > 0 ? max(0, pos1 - a.window + 1) : 0;
-    // the sink is one more key, with a score of its own and no value; in decode it belongs to the first
-    // piece's first warp pair
-    const bool has_sink = a.sinks != nullptr && (PREFILL || (blockIdx.z == 0 && pair == 0));
+    // the sink is one more key, with a score of its own and no value
+    const bool has_sink = a.sinks != nullptr;
     float m_run[2], l_run[2];
-    m_run[0] = has_sink && rv0 ? a.sinks[h0] * LOG2E : -INFINITY;
-    m_run[1] = has_sink && rv1 ? a.sinks[h1] * LOG2E : -INFINITY;
+    m_run[0] = has_sink && rv0 ? a.sinks[head0] * LOG2E : -INFINITY;
+    m_run[1] = has_sink && rv1 ? a.sinks[head0] * LOG2E : -INFINITY;
     l_run[0] = has_sink && rv0 ? 1.f : 0.f;
     l_run[1] = has_sink && rv1 ? 1.f : 0.f;
     float oacc[NO][4];
@@ -178,8 +141,8 @@ __global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const
 #pragma unroll
         for (int e = 0; e < 4; ++e) oacc[n][e] = 0.f;
     const float scale_log2 = a.scale * LOG2E;
-    const int key_off = PREFILL ? half * 32 : pair * 16;     // the keys within a stage whose scores this warp forms
-    // prompts: where the two warps of a pair exchange maxima and weights, 8 words a lane
+    const int key_off = half * 32;                           // the keys within a stage whose scores this warp forms
+    // where the two warps of a pair exchange maxima and weights, 8 words a lane
     float* xch = reinterpret_cast<float*>(kbuf + (size_t)2 * LF_BN * stride);
     float* xw = xch + ((pair * 2 + half) * 32 + lane) * 8;
     const float* xo = xch + ((pair * 2 + (half ^ 1)) * 32 + lane) * 8;
@@ -233,14 +196,13 @@ __global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        if (PREFILL) {     // the other warp of the pair has the maxima of the stage's other 32 keys
-            xw[0] = mx0;
-            xw[1] = mx1;
-            pair_barrier(pair);
-            mx0 = fmaxf(mx0, xo[0]);
-            mx1 = fmaxf(mx1, xo[1]);
-            pair_barrier(pair);
-        }
+        // the other warp of the pair has the maxima of the stage's other 32 keys
+        xw[0] = mx0;
+        xw[1] = mx1;
+        pair_barrier(pair);
+        mx0 = fmaxf(mx0, xo[0]);
+        mx1 = fmaxf(mx1, xo[1]);
+        pair_barrier(pair);
         const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
         const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
         const float corr0 = exp2f(m_run[0] - ms0), corr1 = exp2f(m_run[1] - ms1);
@@ -253,9 +215,9 @@ __global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const
             pown[kk][2] = pack_bf16(exp2f(sacc[2 * kk + 1][0] - ms0), exp2f(sacc[2 * kk + 1][1] - ms0));
             pown[kk][3] = pack_bf16(exp2f(sacc[2 * kk + 1][2] - ms1), exp2f(sacc[2 * kk + 1][3] - ms1));
         }
-        constexpr int PK = PREFILL ? 4 : 1;         // blocks of 16 keys in the value product
+        constexpr int PK = 4;                       // blocks of 16 keys in the value product
         uint32_t pall[PK][4];
-        if (PREFILL) {
+        {
             uint32_t* xwu = reinterpret_cast<uint32_t*>(xw);
             const uint32_t* xou = reinterpret_cast<const uint32_t*>(xo);
 #pragma unroll
@@ -273,9 +235,6 @@ __global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
                     pall[kk][e] = (kk >> 1) == half ? pown[kk % (NT / 2)][e] : poth[kk % (NT / 2)][e];
-        } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) pall[0][e] = pown[0][e];
         }
         // the row sums are taken over the rounded weights, in key order, so that both warps of a pair
         // (and numerator and denominator) see the same numbers
@@ -304,7 +263,7 @@ __global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const
             oacc[n][2] *= corr1;
             oacc[n][3] *= corr1;
         }
-        const bf16* vs_ = PREFILL ? kst : ks_;      // the keys whose values this warp sums
+        const bf16* vs_ = kst;                      // the values of all 64 keys
 #pragma unroll
         for (int kk = 0; kk < PK; ++kk) {
 #pragma unroll
@@ -320,102 +279,19 @@ __global__ __launch_bounds__(PREFILL ? 256 : 128) void latent_flash_kernel(const
         stage ^= 1;
     }
 
-    if (PREFILL) {
-        const float inv0 = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f;
-        const float inv1 = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
-        if (rv0) {
-            bf16* o = a.out + ((size_t)(q_row0 + row_base + g) * nh + head0) * DV + col0;
+    const float inv0 = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f;
+    const float inv1 = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
+    if (rv0) {
+        bf16* o = a.out + ((size_t)(q_row0 + row_base + g) * nh + head0) * DV + col0;
 #pragma unroll
-            for (int n = 0; n < NO; ++n)
-                *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(oacc[n][0] * inv0, oacc[n][1] * inv0);
-        }
-        if (rv1) {
-            bf16* o = a.out + ((size_t)(q_row0 + row_base + g + 8) * nh + head0) * DV + col0;
-#pragma unroll
-            for (int n = 0; n < NO; ++n)
-                *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(oacc[n][2] * inv1, oacc[n][3] * inv1);
-        }
-        pdl_trigger();
-        return;
+        for (int n = 0; n < NO; ++n)
+            *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(oacc[n][0] * inv0, oacc[n][1] * inv0);
     }
-
-    // decode: merge the four warp pairs (their keys differ) through shared memory, which the key
-    // stages no longer need: ml [4 pairs][16 rows][2], then sums [16][DV] float32
-    float* ml = reinterpret_cast<float*>(kbuf);
-    float* osum = ml + PAIRS * 16 * 2;
-    if (half == 0 && c == 0) {
-        ml[(pair * 16 + g) * 2] = m_run[0];
-        ml[(pair * 16 + g) * 2 + 1] = l_run[0];
-        ml[(pair * 16 + g + 8) * 2] = m_run[1];
-        ml[(pair * 16 + g + 8) * 2 + 1] = l_run[1];
-    }
-    __syncthreads();
-    float mg0 = -INFINITY, mg1 = -INFINITY;
+    if (rv1) {
+        bf16* o = a.out + ((size_t)(q_row0 + row_base + g + 8) * nh + head0) * DV + col0;
 #pragma unroll
-    for (int p = 0; p < PAIRS; ++p) {
-        mg0 = fmaxf(mg0, ml[(p * 16 + g) * 2]);
-        mg1 = fmaxf(mg1, ml[(p * 16 + g + 8) * 2]);
-    }
-    const float ms0 = mg0 == -INFINITY ? 0.f : mg0, ms1 = mg1 == -INFINITY ? 0.f : mg1;
-    float lg0 = 0.f, lg1 = 0.f;
-#pragma unroll
-    for (int p = 0; p < PAIRS; ++p) {
-        lg0 += ml[(p * 16 + g) * 2 + 1] * exp2f(ml[(p * 16 + g) * 2] - ms0);
-        lg1 += ml[(p * 16 + g + 8) * 2 + 1] * exp2f(ml[(p * 16 + g + 8) * 2] - ms1);
-    }
-    const float w0 = exp2f(m_run[0] - ms0), w1 = exp2f(m_run[1] - ms1);
-    for (int p = 0; p < PAIRS; ++p) {
-        if (pair == p) {
-#pragma unroll
-            for (int n = 0; n < NO; ++n) {
-                float* r0 = osum + g * DV + col0 + n * 8 + 2 * c;
-                float* r1 = osum + (g + 8) * DV + col0 + n * 8 + 2 * c;
-                if (p == 0) {
-                    r0[0] = oacc[n][0] * w0; r0[1] = oacc[n][1] * w0;
-                    r1[0] = oacc[n][2] * w1; r1[1] = oacc[n][3] * w1;
-                } else {
-                    r0[0] += oacc[n][0] * w0; r0[1] += oacc[n][1] * w0;
-                    r1[0] += oacc[n][2] * w1; r1[1] += oacc[n][3] * w1;
-                }
-            }
-        }
-        __syncthreads();
-    }
-    // rows (heads) x DV sums are complete; every thread takes a share of the columns
-    if (a.pieces == 1) {
-        if (pair == 0) {       // the two warps of pair 0 hold (mg, lg) of rows g and g + 8 in their lanes
-            const float inv0 = lg0 > 0.f ? 1.0f / lg0 : 0.f, inv1 = lg1 > 0.f ? 1.0f / lg1 : 0.f;
-            if (rv0) {
-                bf16* o = a.out + ((size_t)q_row0 * nh + h0) * DV + col0;
-                const float* r = osum + g * DV + col0;
-#pragma unroll
-                for (int n = 0; n < NO; ++n)
-                    *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(r[n * 8 + 2 * c] * inv0, r[n * 8 + 2 * c + 1] * inv0);
-            }
-            if (rv1) {
-                bf16* o = a.out + ((size_t)q_row0 * nh + h1) * DV + col0;
-                const float* r = osum + (g + 8) * DV + col0;
-#pragma unroll
-                for (int n = 0; n < NO; ++n)
-                    *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(r[n * 8 + 2 * c] * inv1, r[n * 8 + 2 * c + 1] * inv1);
-            }
-        }
-    } else {
-        float* part = a.scratch + (((size_t)blockIdx.y * gridDim.x + blockIdx.x) * a.pieces + blockIdx.z) * 16 * (DV + 2);
-        if (pair == 0) {
-            float* p0 = part + g * (DV + 2);
-            float* p1 = part + (g + 8) * (DV + 2);
-            if (half == 0 && c == 0) {
-                p0[DV] = mg0; p0[DV + 1] = lg0;
-                p1[DV] = mg1; p1[DV + 1] = lg1;
-            }
-#pragma unroll
-            for (int n = 0; n < NO; ++n) {
-                const int col = col0 + n * 8 + 2 * c;
-                p0[col] = osum[g * DV + col]; p0[col + 1] = osum[g * DV + col + 1];
-                p1[col] = osum[(g + 8) * DV + col]; p1[col + 1] = osum[(g + 8) * DV + col + 1];
-            }
-        }
+        for (int n = 0; n < NO; ++n)
+            *reinterpret_cast<uint32_t*>(o + n * 8 + 2 * c) = pack_bf16(oacc[n][2] * inv1, oacc[n][3] * inv1);
     }
     pdl_trigger();
 }
@@ -704,23 +580,20 @@ __global__ void latent_merge_kernel(const float* __restrict__ scratch, bf16* __r
     }
 }
 
-template <bool PREFILL> size_t latent_smem_bytes(int dk, int dv) {
-    const size_t stages = (size_t)((PREFILL ? 64 : 16) + 2 * (PREFILL ? 64 : 32)) * (dk + 8) * sizeof(bf16) +
-                          (PREFILL ? (size_t)256 * 8 * sizeof(float) : 0);
-    const size_t merge = PREFILL ? 0 : (size_t)16 * (dk + 8) * sizeof(bf16) + (2 * 16 * 2 + (size_t)16 * dv) * sizeof(float);
-    return stages > merge ? stages : merge;
+static size_t latent_smem_bytes(int dk) {      // queries, two stages of keys, the pairs' exchange words
+    return (size_t)(64 + 2 * 64) * (dk + 8) * sizeof(bf16) + (size_t)256 * 8 * sizeof(float);
 }
 
-template <int DV, bool PREFILL>
-int launch_latent(const LatentArgs& a, dim3 grid, int dv, cudaStream_t stream) {
-    const size_t smem = latent_smem_bytes<PREFILL>(a.dk, dv);
+template <int DV>
+int launch_latent(const LatentArgs& a, dim3 grid, cudaStream_t stream) {
+    const size_t smem = latent_smem_bytes(a.dk);
     if (smem > 227 * 1024) return RLIS_ERR_UNSUPPORTED;      // 232,448 bytes: the most a CTA can ask for
     static size_t allowed = 0;
     if (smem > allowed) {
-        cudaFuncSetAttribute(latent_flash_kernel<DV, PREFILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(latent_flash_kernel<DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         allowed = smem;
     }
-    rlis_launch(latent_flash_kernel<DV, PREFILL>, grid, PREFILL ? 256 : 128, smem, stream, a);
+    rlis_launch(latent_flash_kernel<DV>, grid, 256, smem, stream, a);
     return RLIS_LAUNCH_CHECK();
 }
 }  // namespace
@@ -729,7 +602,7 @@ int launch_latent(const LatentArgs& a, dim3 grid, int dv, cudaStream_t stream) {
 // that are multiples of 16 entries and fit shared memory with two stages of keys.
 extern "C" int rlis_attention_latent_mma_takes(int dk, int dv) {
     if (!(dv == 64 || dv == 128 || dv == 256 || dv == 512) || dk % 16 || dk < dv || dk <= 0) return 0;
-    return latent_smem_bytes<true>(dk, dv) <= 227 * 1024 ? 1 : 0;
+    return latent_smem_bytes(dk) <= 227 * 1024 ? 1 : 0;
 }
 
 extern "C" int rlis_attention_latent_prefill(const void* qa, int q_bf16, const void* cache, void* out, const float* sinks,
@@ -743,10 +616,10 @@ extern "C" int rlis_attention_latent_prefill(const void* qa, int q_bf16, const v
                     nullptr, nullptr, max_blocks, nh, dk, page_size, window, 1, 0, scale, q_bf16};
     dim3 grid(nh, n_tiles);
     switch (dv) {
-        case 64: return launch_latent<64, true>(a, grid, dv, stream);
-        case 128: return launch_latent<128, true>(a, grid, dv, stream);
-        case 256: return launch_latent<256, true>(a, grid, dv, stream);
-        default: return launch_latent<512, true>(a, grid, dv, stream);
+        case 64: return launch_latent<64>(a, grid, stream);
+        case 128: return launch_latent<128>(a, grid, stream);
+        case 256: return launch_latent<256>(a, grid, stream);
+        default: return launch_latent<512>(a, grid, stream);
     }
 }
 

@@ -47,10 +47,21 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
     float* S = state + (((size_t)slot * nh + h) * dv + c0 + col) * d;    // this thread's column: d contiguous entries
     const float g = decay[h];
     float s[E];
+    const bool quads = d % 4 == 0;                 // a thread's entries are then whole 16-byte vectors
+    if (quads) {
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-        const int i = slice * E + e;
-        s[e] = (!fresh && live && i < d) ? S[i] : 0.f;
+        for (int e = 0; e < E; e += 4) {
+            const int i = slice * E + e;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (!fresh && live && i < d) v = *reinterpret_cast<const float4*>(S + i);
+            s[e] = v.x; s[e + 1] = v.y; s[e + 2] = v.z; s[e + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const int i = slice * E + e;
+            s[e] = (!fresh && live && i < d) ? S[i] : 0.f;
+        }
     }
     // what one thread stages of q and k: element idx = threadIdx.x + j * THREADS of the [TOK][DP] tile
     constexpr int PER = TOK * DP / THREADS;
@@ -124,7 +135,13 @@ __global__ __launch_bounds__(THREADS) void lightning_scan_kernel(
             if (c0 + c < dv) out[(size_t)(row0 + t0 + tt) * nh * dv + h * dv + c0 + c] = sum;
         }
     }
-    if (live) {
+    if (live && quads) {
+#pragma unroll
+        for (int e = 0; e < E; e += 4) {
+            const int i = slice * E + e;
+            if (i < d) *reinterpret_cast<float4*>(S + i) = make_float4(s[e], s[e + 1], s[e + 2], s[e + 3]);
+        }
+    } else if (live) {
 #pragma unroll
         for (int e = 0; e < E; ++e) {
             const int i = slice * E + e;
