@@ -4,6 +4,7 @@
 // value sum is taken over the latent part of the rows; the caller applies W_uv afterwards.
 //
 //   latent_kv_store : row = [ z[:r] / sqrt(mean(z[:r]^2) + eps) * w | rotate(z[r:]) ] -> paged cache
+//                     (and, for the layer that projects both latents at once, the query latent's norm)
 //   latent_q_rope   : qa[t, h, r:] = rotate(q[t, h, d:]), float32 (or bfloat16 for the tensor-core kernels)
 //   attention_latent: softmax over keys 0..pos (or the last `window`), optionally with one more
 //                     term exp(sink_h) in the denominator that has no value
@@ -24,10 +25,23 @@ template <typename T>
 __global__ __launch_bounds__(128) void latent_kv_store_kernel(
     const T* __restrict__ z, long long z_stride, const float* __restrict__ w, const float* __restrict__ inv_freq,
     const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ cache, int rank,
-    int rot_width, int rot_dims, float mag, float eps) {
+    int rot_width, int rot_dims, float mag, float eps, const T* __restrict__ zq, const float* __restrict__ wq,
+    T* __restrict__ cq, int q_rank) {
     pdl_wait_and_trigger();
     __shared__ float scratch[33];
     const int t = blockIdx.x;
+    if (zq != nullptr) {      // the query latent of the same projection's row: cq = rmsnorm(zq) * wq
+        const T* qr = zq + (size_t)t * z_stride;
+        float sq = 0.f;
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
+            const float v = to_f<T>(qr[i]);
+            sq = fmaf(v, v, sq);
+        }
+        sq = block_sum(sq, scratch);
+        const float rq = 1.0f / sqrtf(sq / (float)q_rank + eps);
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+            cq[(size_t)t * q_rank + i] = from_f<T>(to_f<T>(qr[i]) * rq * wq[i]);
+    }
     const T* zr = z + (size_t)t * z_stride;
     float ss = 0.f;
     for (int i = threadIdx.x; i < rank; i += blockDim.x) {
@@ -174,18 +188,21 @@ __global__ __launch_bounds__(WARPS * 32) void attention_latent_kernel(
 }
 }  // namespace
 
+// zq != null: also cq[t, :] = rmsnorm(zq[t, :q_rank]) * wq (same eps), zq rows z_stride apart like z's.
 extern "C" int rlis_latent_kv_store(const void* z, long long z_stride, const float* w, const float* inv_freq,
                                     const int* positions, const int* slots, void* cache, int n_tokens, int rank,
-                                    int rot_width, int rot_dims, float mag, float eps, int dtype,
-                                    cudaStream_t stream) {
+                                    int rot_width, int rot_dims, float mag, float eps, int dtype, const void* zq,
+                                    const float* wq, void* cq, int q_rank, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rank <= 0 || rot_width < 0 || rot_dims < 0 || rot_dims > rot_width || rot_dims % 2) return RLIS_ERR_UNSUPPORTED;
     if (dtype == RLIS_F32)
         rlis_launch(latent_kv_store_kernel<float>, n_tokens, 128, 0, stream, (const float*)z, z_stride, w, inv_freq,
-                    positions, slots, (float*)cache, rank, rot_width, rot_dims, mag, eps);
+                    positions, slots, (float*)cache, rank, rot_width, rot_dims, mag, eps, (const float*)zq, wq, (float*)cq,
+                    q_rank);
     else if (dtype == RLIS_BF16)
         rlis_launch(latent_kv_store_kernel<bf16>, n_tokens, 128, 0, stream, (const bf16*)z, z_stride, w, inv_freq,
-                    positions, slots, (bf16*)cache, rank, rot_width, rot_dims, mag, eps);
+                    positions, slots, (bf16*)cache, rank, rot_width, rot_dims, mag, eps, (const bf16*)zq, wq, (bf16*)cq,
+                    q_rank);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

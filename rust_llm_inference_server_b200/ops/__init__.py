@@ -283,11 +283,23 @@ def bias_act(x: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, acti
 
 def latent_kv_store(z: torch.Tensor, weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, rot_dims: int,
                     magnitude: float, positions: torch.Tensor, slots: torch.Tensor, cache: torch.Tensor,
-                    rank: int, page_size: int) -> None:
+                    rank: int, page_size: int, q_latent: torch.Tensor | None = None,
+                    q_weight: torch.Tensor | None = None, q_out: torch.Tensor | None = None) -> None:
     """Writes one row per token into a paged cache of latents [pages, 1, page_size, rank + rot]:
     rmsnorm(z[:, :rank]) * weight, then z[:, rank:] with its first `rot_dims` entries rotated
-    (rotate-half, angle position * inv_freq, cos and sin times `magnitude`).  z may be a column slice."""
+    (rotate-half, angle position * inv_freq, cos and sin times `magnitude`).  z may be a column slice.
+    With `q_latent` (another column slice of the same rows), `q_weight` and `q_out` [T, q_rank]
+    (contiguous) the same launch also leaves q_out = rmsnorm(q_latent) * q_weight."""
     T, Wd = z.shape
+    zq = wq = cq = None
+    q_rank = 0
+    if q_latent is not None:
+        q_rank = q_latent.shape[1]
+        if q_latent.dtype != z.dtype or q_latent.stride(0) != z.stride(0) or q_latent.stride(1) != 1 or q_latent.shape[0] != T:
+            raise KernelError("latent_kv_store: the query latent must be a column slice of the same rows as z")
+        _req(q_weight, "q_weight", torch.float32, (q_rank,))
+        _req(q_out, "q_out", z.dtype, (T, q_rank))
+        zq, wq, cq = q_latent.data_ptr(), q_weight.data_ptr(), q_out.data_ptr()
     rot = Wd - rank
     if not z.is_cuda or z.stride(1) != 1 or rot < 0:
         raise KernelError("latent_kv_store: z must be [T, rank + rot] rows on the device with unit stride")
@@ -298,9 +310,10 @@ def latent_kv_store(z: torch.Tensor, weight: torch.Tensor, eps: float, inv_freq:
     _req(cache, "cache", z.dtype, (None, 1, page_size, Wd))
     check(lib().rlis_latent_kv_store(z.data_ptr(), z.stride(0), weight.data_ptr(), inv_freq.data_ptr(),
                                      positions.data_ptr(), slots.data_ptr(), cache.data_ptr(), T, rank, rot,
-                                     int(rot_dims), float(magnitude), float(eps), _code(z.dtype), _stream()),
+                                     int(rot_dims), float(magnitude), float(eps), _code(z.dtype), zq, wq, cq, q_rank,
+                                     _stream()),
           "latent_kv_store")
-    _count("latent_kv_store")
+    _count("latent_kv_store" + (".q_norm" if q_latent is not None else ""))
 
 
 def latent_q_rope(q: torch.Tensor, qa: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int, magnitude: float,

@@ -32,7 +32,7 @@ SIGNATURES = {
     "rlis_post_norm_residual": [P, P, P, P, P, P, P, I, I, F, F, I, P],
     "rlis_act_norm": [P, LL, I, P, P, LL, P, LL, I, I, F, I, P],
     "rlis_bias_act": [P, P, P, LL, I, I, I, P],
-    "rlis_latent_kv_store": [P, LL, P, P, P, P, P, I, I, I, I, F, F, I, P],
+    "rlis_latent_kv_store": [P, LL, P, P, P, P, P, I, I, I, I, F, F, I, P, P, P, I, P],
     "rlis_latent_q_rope": [P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "rlis_attention_latent": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "rlis_attention_latent_mma_takes": [I, I],

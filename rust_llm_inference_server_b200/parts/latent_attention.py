@@ -90,14 +90,17 @@ class LatentAttention(Mixer):
         dk = s.kv_rank + s.rot_dim
         with span("latent down proj"):
             down = ops.linear(x, self.w_down)
+        cq = step.buffer("latent_cq", (T, s.q_rank), self.dtype)
         if self.own_kv and writes_cache:
-            with span("latent norm + rope + cache write"):
+            # one launch: the kv latent's norm, the shared key part's rotation, the paged write, and the
+            # query latent's norm
+            with span("latent norms + rope + cache write"):
                 ops.latent_kv_store(down[:, s.q_rank:], self.kv_norm, self.eps, self.inv_freq, self.rot_dims,
                                     self.magnitude, step.positions, step.slots[cache.group], cache.k, s.kv_rank,
-                                    cache.page_size)
-        with span("q latent norm"):
-            cq = ops.act_norm(down[:, :s.q_rank], self.q_norm, self.eps,
-                              step.buffer("latent_cq", (T, s.q_rank), self.dtype))
+                                    cache.page_size, q_latent=down[:, :s.q_rank], q_weight=self.q_norm, q_out=cq)
+        else:
+            with span("q latent norm"):
+                ops.act_norm(down[:, :s.q_rank], self.q_norm, self.eps, cq)
         with span("q up proj"):
             q = ops.linear(cq, self.w_q_up)
         # float32, or bfloat16 when the whole step goes to the tensor-core attention kernels

@@ -136,8 +136,13 @@ def test_latent_rows_are_normed_rotated_and_stored(dtype, rank, rot, dims):
     z = dev(rng.standard_normal((T, lead + rank + rot)), dtype)
     w = dev(1 + 0.3 * rng.standard_normal(rank))
     cache = torch.zeros((6, 1, page, rank + rot), dtype=dtype, device="cuda")
+    wq = dev(1 + 0.3 * rng.standard_normal(lead))
+    cq = torch.empty((T, lead), dtype=dtype, device="cuda")
     ops.latent_kv_store(z[:, lead:], w, 1e-5, dev(f), dims, mag, dev(positions, torch.int32), dev(slots, torch.int32),
-                        cache, rank, page)
+                        cache, rank, page, q_latent=z[:, :lead], q_weight=wq, q_out=cq)    # the leading columns as a query latent
+    np.testing.assert_allclose(cq.float().cpu().numpy(),
+                               P.plain_norm(z[:, :lead].double().cpu().numpy(), wq.double().cpu().numpy(), 1e-5),
+                               rtol=0, atol=3e-5 if dtype == torch.float32 else 3e-2)
     zz = z[:, lead:].double().cpu().numpy()
     cos, sin = P.rotary_table(rcfg, 702)
     want = np.concatenate([P.plain_norm(zz[:, :rank], w.double().cpu().numpy(), 1e-5),
@@ -405,8 +410,11 @@ def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, page, lens
         worst = max(position_error(v, results["whole"][k]) for k, v in results[fam].items())
         assert worst <= TOL_BETWEEN[dtype], f"{which} {dtype}: {fam} differs from whole by {worst}"
     fast = dtype == "bfloat16" and which == "Z"
-    for k in (("attention_latent.decode.mma", "attention_latent.prefill.mma") if fast else ("attention_latent",)) + ("lightning_scan", "latent_kv_store", "latent_q_rope", "post_norm_residual",
-              "post_norm_residual.next", "act_norm", "act_norm.gate", "bias_act.relu2"):
+    reads_other = any("kv_from" in l["mixer"] for l in U.CONFIGS[which]["layers"])
+    for k in (("attention_latent.decode.mma", "attention_latent.prefill.mma") if fast else ("attention_latent",)) + \
+            (("act_norm",) if reads_other else ()) + \
+            ("lightning_scan", "lightning_scan.silu_pass", "latent_kv_store.q_norm", "latent_q_rope", "post_norm_residual",
+             "post_norm_residual.next", "act_norm.gate", "bias_act.relu2"):
         assert ops.launches_by_kernel.get(k), f"never launched {k}; launched {sorted(ops.launches_by_kernel)}"
 
 
