@@ -16,7 +16,7 @@
 #include <math.h>
 
 namespace {
-constexpr int COLS = 16, SLICES = 16, MAX_E = 16;   // d up to 256
+constexpr int COLS = 16, SLICES = 16, MAX_E = 32;   // d up to 512
 constexpr int THREADS = COLS * SLICES;
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
@@ -174,7 +174,8 @@ int launch_scan(const T* proj, long long stride, int q_off, int k_off, int v_off
                                  v_off, out, state, decay, cu, ctx, slots, nh, d, dv)
     if (e <= 4) RLIS_SCAN(4);
     else if (e <= 8) RLIS_SCAN(8);
-    else RLIS_SCAN(16);
+    else if (e <= 16) RLIS_SCAN(16);
+    else RLIS_SCAN(32);
 #undef RLIS_SCAN
     return RLIS_LAUNCH_CHECK();
 }

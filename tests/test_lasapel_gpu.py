@@ -306,7 +306,7 @@ def test_tensor_core_attention_over_latents(H, rank, rot, window, use_sinks):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,d,dv", [(2, 24, 40), (1, 8, 48), (3, 128, 16), (2, 200, 8)])
+@pytest.mark.parametrize("H,d,dv", [(2, 24, 40), (1, 8, 48), (3, 128, 16), (2, 200, 8), (1, 320, 24)])
 def test_decayed_recurrence_carries_its_state(dtype, H, d, dv):
     from rust_llm_inference_server_b200 import ops
     rng = np.random.default_rng(d)
