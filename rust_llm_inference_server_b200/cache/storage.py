@@ -33,8 +33,14 @@ class CacheGroup:
         """2: keys and values; 1: a single row per token."""
         return 2 if getattr(self.spec, "values", True) else 1
 
+    @property
+    def v_head_dim(self) -> int:
+        """Width of a value row (a key row's unless the spec says otherwise)."""
+        return int(getattr(self.spec, "v_head_dim", None) or self.spec.head_dim)
+
     def bytes_per_page(self, elem_size: int) -> int:
-        return len(self.slots) * self.planes * self.spec.n_kv_heads * self.page_size * self.spec.head_dim * elem_size
+        row = self.spec.head_dim + (self.v_head_dim if self.planes == 2 else 0)
+        return len(self.slots) * self.spec.n_kv_heads * self.page_size * row * elem_size
 
 
 def plan_groups(slot_specs, page_size: int) -> list[CacheGroup]:
@@ -92,8 +98,16 @@ class CacheStorage:
             s = g.spec
             # Zeroed once and never cleared when pages are given back: correctness rests on
             # context lengths and masks, never on page contents (crates/model/src/paged.rs:53-60).
-            pool = torch.zeros((len(g.slots), g.planes, g.num_pages, s.n_kv_heads, g.page_size, s.head_dim),
-                               dtype=dtype, device=device)
+            if g.planes == 2 and g.v_head_dim != s.head_dim:
+                # value rows of another width than key rows: a pool each, [slot in group, page, kv head,
+                # position in page, d]; the same page ids address both
+                pool = (torch.zeros((len(g.slots), g.num_pages, s.n_kv_heads, g.page_size, s.head_dim),
+                                    dtype=dtype, device=device),
+                        torch.zeros((len(g.slots), g.num_pages, s.n_kv_heads, g.page_size, g.v_head_dim),
+                                    dtype=dtype, device=device))
+            else:
+                pool = torch.zeros((len(g.slots), g.planes, g.num_pages, s.n_kv_heads, g.page_size, s.head_dim),
+                                   dtype=dtype, device=device)
             self.pools.append(pool)
             for i, slot in enumerate(g.slots):
                 self._slot_home[slot] = (gi, i)
@@ -110,7 +124,9 @@ class CacheStorage:
             return None
         gi, i = self._slot_home[slot]
         pool = self.pools[gi]
+        if isinstance(pool, tuple):
+            return LayerCache(pool[0][i], pool[1][i], gi, self.groups[gi].page_size)
         return LayerCache(pool[i, 0], pool[i, 1] if pool.shape[1] > 1 else None, gi, self.groups[gi].page_size)
 
     def bytes(self) -> int:
-        return sum(p.numel() * p.element_size() for p in self.pools)
+        return sum(t.numel() * t.element_size() for p in self.pools for t in (p if isinstance(p, tuple) else (p,)))

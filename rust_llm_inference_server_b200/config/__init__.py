@@ -1,4 +1,5 @@
 from .engine_config import EngineConfig
+from .gavodra_config import GavodraConfig
 from .lasapel_config import LasapelConfig
 from .model_config import ConfigError, LlamaConfig, RopeScaling, read_config_json
 from .registry import (architecture_name, lookup_architecture, register_architecture,

@@ -1,0 +1,220 @@
+// Causal grouped-query attention with per-head RMS-normed queries and keys, a learned bias by
+// distance, values of their own width, optional mixing of a layer's values with another layer's,
+// and a gate on every head's output.  No rotation: positions enter through the bias alone.
+//
+//   q_h = rmsnorm(q_h) * wq,  k_g = rmsnorm(k_g) * wk              (weights shared by the heads)
+//   v_g = (1 - lambda) v_g + lambda v_other_g                      (where a layer mixes; that is what is cached)
+//   score(i, j) = scale * q_h(i) . k_g(j) + bias[min(i - j, n_dist - 1), h],  j <= i (and i - j < window)
+//   out_h(i) = sigmoid(gate_h(i)) * sum_j softmax_j(score) v_g(j)
+//
+// `bias` is a float32 table [n_dist, n_heads] by distance (the host turns bucket rules into it; all
+// distances from n_dist - 1 on share the last row).  Norms, scores, softmax, value sums, the mixing and
+// the gate are float32 whatever the element type.
+//
+// norm_store: one warp per (token, query or key/value head); writes normed queries to q_out and
+// normed keys and (mixed) values into the paged cache [page, kv head, slot in page, d | dv].
+// attention: one warp per (token, query head), keys in blocks of 32 that start at multiples of 32, so
+// the order of every sum depends on the query's position only.  The kernel of the float32 path and
+// the fallback of the bfloat16 path for sizes the tensor-core kernels refuse.
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+constexpr int WARPS = 4;
+constexpr int MAX_D = 256;     // head sizes up to 256 (8 entries a lane)
+
+template <typename T>
+__global__ __launch_bounds__(WARPS * 32) void qk_norm_store_kernel(
+    const T* __restrict__ proj, long long stride, int q_off, int k_off, int v_off,
+    const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+    const T* __restrict__ v_other, long long v_other_stride, float lambda,
+    T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ slots,
+    int n_units, int nh, int nkv, int d, int dv, int page_size) {
+    pdl_wait_and_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * WARPS + warp;
+    if (unit >= n_units) return;
+    const int per = nh + nkv;
+    const int t = unit / per, u = unit - t * per;
+    const T* row = proj + (size_t)t * stride;
+    const bool is_q = u < nh;
+    const T* x = row + (is_q ? q_off + u * d : k_off + (u - nh) * d);
+    const float* w = is_q ? q_w : k_w;
+    float v[MAX_D / 32];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) {
+        const int c = lane + 32 * i;
+        v[i] = c < d ? to_f<T>(x[c]) : 0.f;
+        ss = fmaf(v[i], v[i], ss);
+    }
+    ss = warp_sum(ss);
+    const float r = w != nullptr ? 1.0f / sqrtf(ss / (float)d + eps) : 1.0f;
+    T* dst = nullptr;
+    long long vrow = -1;
+    if (is_q) {
+        dst = q_out + ((size_t)t * nh + u) * d;
+    } else {
+        const int slot = slots != nullptr ? slots[t] : -1;
+        if (slot >= 0) {
+            const long long page = slot / page_size;
+            const int off = slot % page_size;
+            const long long r0 = (page * nkv + (u - nh)) * page_size + off;
+            dst = k_cache + r0 * d;
+            vrow = r0 * dv;
+        }
+    }
+    if (dst != nullptr) {
+#pragma unroll
+        for (int i = 0; i < MAX_D / 32; ++i) {
+            const int c = lane + 32 * i;
+            if (c < d) dst[c] = from_f<T>(w != nullptr ? v[i] * r * w[c] : v[i]);
+        }
+    }
+    if (vrow >= 0) {
+        const int g = u - nh;
+        const T* vs = row + v_off + g * dv;
+        const T* vo = v_other != nullptr ? v_other + (size_t)t * v_other_stride + g * dv : nullptr;
+        for (int c = lane; c < dv; c += 32) {
+            float val = to_f<T>(vs[c]);
+            if (vo != nullptr) val = (1.0f - lambda) * val + lambda * to_f<T>(vo[c]);
+            v_cache[vrow + c] = from_f<T>(val);
+        }
+    }
+}
+
+template <typename T>
+__global__ __launch_bounds__(WARPS * 32) void attn_bias_kernel(
+    const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
+    const float* __restrict__ bias, int n_dist, const T* __restrict__ gate, long long gate_stride,
+    const int* __restrict__ seq_of_token, const int* __restrict__ positions, const int* __restrict__ block_tables,
+    const int* __restrict__ token_rows, int max_blocks, int n_rows, int nh, int nkv, int d, int dv, int page_size,
+    float scale, int window) {
+    pdl_wait();
+    extern __shared__ float qs_all[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gw = blockIdx.x * WARPS + warp;
+    if (gw >= n_rows) return;  // no block-wide barrier below
+    const int ti = gw / nh, h = gw - ti * nh;
+    const int t = token_rows != nullptr ? token_rows[ti] : ti;
+    const int kvh = h / (nh / nkv);
+    const int pos = positions[t];
+    const int* table = block_tables + (size_t)seq_of_token[t] * max_blocks;
+    float* qs = qs_all + warp * d;
+    const T* qrow = q + ((size_t)t * nh + h) * d;
+    for (int j = lane; j < d; j += 32) qs[j] = to_f<T>(qrow[j]);
+    __syncwarp();
+
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    float m = -INFINITY, l = 0.f;
+    float acc[MAX_D / 32];
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
+
+    for (int kb = lo - (lo & 31); kb <= pos; kb += 32) {
+        const int key = kb + lane;
+        const bool valid = key >= lo && key <= pos;
+        float s = -INFINITY;
+        long long row = -1;      // row of this lane's key in the pools, or -1: hidden, or a page the host did not map
+        if (valid) {
+            const int page = table[key / page_size];
+            if (page < 0) {
+                s = NAN;
+            } else {
+                row = ((long long)page * nkv + kvh) * page_size + key % page_size;
+                const T* krow = k_cache + row * d;
+                float dot = 0.f;
+                for (int j = 0; j < d; ++j) dot = fmaf(qs[j], to_f<T>(krow[j]), dot);
+                s = dot * scale;
+                if (bias != nullptr) s += bias[(size_t)min(pos - key, n_dist - 1) * nh + h];
+            }
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float p = valid ? expf(s - m_new) : 0.f;
+        const float corr = expf(m - m_new);
+        l = l * corr + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= corr;
+#pragma unroll 8
+        for (int kk = 0; kk < 32; ++kk) {
+            const float pk = __shfl_sync(0xffffffffu, p, kk);
+            const long long r = __shfl_sync(0xffffffffu, row, kk);
+            const bool use = pk != 0.f && r >= 0;  // uniform over the warp
+            const T* vrow = v_cache + (use ? r * dv : 0);
+#pragma unroll
+            for (int i = 0; i < MAX_D / 32; ++i) {
+                const int c = lane + 32 * i;
+                if (c < dv) {
+                    const float v = to_f<T>(vrow[c]);
+                    acc[i] = use ? fmaf(pk, v, acc[i]) : acc[i];
+                }
+            }
+        }
+        m = m_new;
+    }
+    float g = 1.0f;
+    if (gate != nullptr) g = 1.0f / (1.0f + expf(-to_f<T>(gate[(size_t)t * gate_stride + h])));
+    T* orow = out + ((size_t)t * nh + h) * dv;
+    const float inv_l = g / l;
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) {
+        const int c = lane + 32 * i;
+        if (c < dv) orow[c] = from_f<T>(acc[i] * inv_l);
+    }
+    pdl_trigger();
+}
+}  // namespace
+
+// proj [T, stride]: the stacked projection's rows; queries at column q_off (nh heads of d), keys at
+// k_off (nkv of d), values at v_off (nkv of dv).  q_w, k_w float32 [d] (null: no norm).  v_other (null:
+// no mixing): rows of another layer's values [T, v_other_stride], mixed in with weight lambda.
+// slots null: nothing is stored (the call reads another call's cache) and only q_out is made.
+extern "C" int rlis_qk_norm_store(const void* proj, long long stride, int q_off, int k_off, int v_off,
+                                  const float* q_w, const float* k_w, float eps, const void* v_other,
+                                  long long v_other_stride, float lambda, void* q_out, void* k_cache, void* v_cache,
+                                  const int* slots, int n_tokens, int nh, int nkv, int d, int dv, int page_size,
+                                  int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (d <= 0 || d > MAX_D || dv <= 0 || nh <= 0 || nkv <= 0) return RLIS_ERR_UNSUPPORTED;
+    const long long units = (long long)n_tokens * (nh + nkv);
+    if (units > 0x7fffffffLL) return RLIS_ERR_UNSUPPORTED;
+    const unsigned blocks = (unsigned)((units + WARPS - 1) / WARPS);
+    if (dtype == RLIS_F32)
+        rlis_launch(qk_norm_store_kernel<float>, blocks, WARPS * 32, 0, stream, (const float*)proj, stride, q_off, k_off,
+                    v_off, q_w, k_w, eps, (const float*)v_other, v_other_stride, lambda, (float*)q_out, (float*)k_cache,
+                    (float*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size);
+    else if (dtype == RLIS_BF16)
+        rlis_launch(qk_norm_store_kernel<bf16>, blocks, WARPS * 32, 0, stream, (const bf16*)proj, stride, q_off, k_off,
+                    v_off, q_w, k_w, eps, (const bf16*)v_other, v_other_stride, lambda, (bf16*)q_out, (bf16*)k_cache,
+                    (bf16*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size);
+    else
+        return RLIS_ERR_UNSUPPORTED;
+    return RLIS_LAUNCH_CHECK();
+}
+
+// q [T, nh d]; k_cache [pages, nkv, page_size, d]; v_cache [pages, nkv, page_size, dv]; out [T, nh dv];
+// bias float32 [n_dist, nh] or null; gate (null: none): logits, head h of token t at gate[t * gate_stride + h].
+extern "C" int rlis_attention_bias(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                   const float* bias, int n_dist, const void* gate, long long gate_stride,
+                                   const int* seq_of_token, const int* positions, const int* block_tables,
+                                   const int* token_rows, int max_blocks, int n_tokens, int nh, int nkv, int d, int dv,
+                                   int page_size, float scale, int window, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (d <= 0 || d > MAX_D || dv <= 0 || dv > MAX_D || nkv <= 0 || nh % nkv != 0 || (bias != nullptr && n_dist <= 0))
+        return RLIS_ERR_UNSUPPORTED;
+    const long long n_rows = (long long)n_tokens * nh;
+    if (n_rows > 0x7fffffffLL) return RLIS_ERR_UNSUPPORTED;
+    const unsigned blocks = (unsigned)((n_rows + WARPS - 1) / WARPS);
+    const size_t smem = (size_t)WARPS * d * sizeof(float);
+    if (dtype == RLIS_F32)
+        rlis_launch(attn_bias_kernel<float>, blocks, WARPS * 32, smem, stream, (const float*)q, (const float*)k_cache,
+                    (const float*)v_cache, (float*)out, bias, n_dist, (const float*)gate, gate_stride, seq_of_token,
+                    positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, dv, page_size, scale, window);
+    else if (dtype == RLIS_BF16)
+        rlis_launch(attn_bias_kernel<bf16>, blocks, WARPS * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache,
+                    (const bf16*)v_cache, (bf16*)out, bias, n_dist, (const bf16*)gate, gate_stride, seq_of_token,
+                    positions, block_tables, token_rows, max_blocks, (int)n_rows, nh, nkv, d, dv, page_size, scale, window);
+    else
+        return RLIS_ERR_UNSUPPORTED;
+    return RLIS_LAUNCH_CHECK();
+}

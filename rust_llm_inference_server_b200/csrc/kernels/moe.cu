@@ -1,0 +1,309 @@
+// A feed-forward that routes every token to `top` of `n_experts` small gated feed-forwards.
+//
+//   route:   z = W_r h (float32), s = sigmoid(z); the `top` experts with the largest s + correction are
+//            chosen (ties: the lower index); their weights are s * route_scale (no renormalisation).  An
+//            extra row of W_r, where given, is the logit of a gate on a shared expert: sigmoid of it.
+//   align:   the (token, choice) pairs are sorted by expert into slots; every expert's run of slots is
+//            padded to a multiple of the row tile, so a tile of rows belongs to one expert.  All on the
+//            device: no count ever reaches the host, and launches depend on the step's shape only.
+//   up:      act[slot, :] = glu(W_gate_e x, W_up_e x) for the slot's token x and expert e
+//   down:    y[slot, :] = W_down_e act[slot, :]                         (float32)
+//   combine: out[t, :] = sum_k weight[t, k] * y[slot(t, k), :] + shared_gate[t] * shared[t, :]
+//
+// glu(g, u) = g' * sigmoid(slope * g') * (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit).
+//
+// The products here are CUDA-core FFMA over k = 0..K-1 in that order for every output element, in float32
+// whatever the element type, so a token's result does not depend on what else is in the batch; the
+// tensor-core products for bfloat16 are in moe_mma.cu.
+#include "common.cuh"
+#include <math.h>
+
+#define RLIS_MOE_TILE_M 32
+
+namespace {
+constexpr int BM = RLIS_MOE_TILE_M, BN = 64, BK = 16;
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+template <typename T>
+__global__ __launch_bounds__(128) void moe_route_kernel(
+    const T* __restrict__ x, const float* __restrict__ w_router, const float* __restrict__ correction,
+    int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ shared_gate,
+    int width, int n_experts, int top, float route_scale) {
+    pdl_wait_and_trigger();
+    extern __shared__ float sm[];
+    float* z = sm;                          // [n_experts + 1]
+    float* choice = sm + n_experts + 1;     // [n_experts]
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const T* row = x + (size_t)t * width;
+    const int n_rows = n_experts + (shared_gate != nullptr ? 1 : 0);
+    for (int e = warp; e < n_rows; e += nwarps) {
+        const float* w = w_router + (size_t)e * width;
+        float dot = 0.f;
+        for (int k = lane; k < width; k += 32) dot = fmaf(w[k], to_f<T>(row[k]), dot);
+        dot = warp_sum(dot);
+        if (lane == 0) z[e] = dot;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        const float s = sigmoidf_(z[e]);
+        z[e] = s;
+        choice[e] = s + (correction != nullptr ? correction[e] : 0.f);
+    }
+    if (threadIdx.x == 0 && shared_gate != nullptr) shared_gate[t] = sigmoidf_(z[n_experts]);
+    __syncthreads();
+    if (warp != 0) return;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float c = choice[e];
+            if (c > best || (c == best && e < at)) { best = c; at = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at >= n_experts) at = k;        // scores that compare with nothing (NaN): still a valid index
+        if (lane == 0) {
+            top_idx[(size_t)t * top + k] = at;
+            top_w[(size_t)t * top + k] = z[at] * route_scale;
+            choice[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+// One CTA.  pairs = tokens * top.  sorted_pair [max_tiles * BM]: the pair in a slot or -1; pair_slot [pairs];
+// tile_expert [max_tiles]: the expert of a tile of BM slots or -1 (no such tile).
+__global__ __launch_bounds__(1024) void moe_align_kernel(
+    const int* __restrict__ top_idx, int* __restrict__ sorted_pair, int* __restrict__ pair_slot,
+    int* __restrict__ tile_expert, int n_pairs, int n_experts, int max_tiles) {
+    pdl_wait_and_trigger();
+    extern __shared__ int smi[];
+    int* count = smi;                    // [n_experts]
+    int* start = smi + n_experts;        // [n_experts]
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
+    for (int i = threadIdx.x; i < max_tiles * BM; i += blockDim.x) sorted_pair[i] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = top_idx[i];
+        if (e >= 0 && e < n_experts) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tile = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            start[e] = tile * BM;
+            const int tiles = (count[e] + BM - 1) / BM;
+            for (int i = 0; i < tiles && tile < max_tiles; ++i) tile_expert[tile++] = e;
+            count[e] = 0;                // from here on: the next free slot of the expert's run
+        }
+        for (; tile < max_tiles; ++tile) tile_expert[tile] = -1;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = top_idx[i];
+        if (e < 0 || e >= n_experts) { pair_slot[i] = -1; continue; }
+        const int slot = start[e] + atomicAdd(&count[e], 1);
+        if (slot >= max_tiles * BM) { pair_slot[i] = -1; continue; }    // the host sizes max_tiles so that this never happens
+        sorted_pair[slot] = i;
+        pair_slot[i] = slot;
+    }
+}
+
+// GLU true:  out[slot, n] = glu(A[token(slot), :] . Wg[e][n, :], A[token(slot), :] . Wu[e][n, :]), out in T
+// GLU false: out[slot, n] = A[slot, :] . Wg[e][n, :], out float32
+template <typename T, bool GLU>
+__global__ __launch_bounds__(256) void moe_gemm_kernel(
+    const T* __restrict__ A, const T* __restrict__ Wg, const T* __restrict__ Wu, void* __restrict__ out_,
+    const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert, int top, int N, int K,
+    float slope, float limit, float shift) {
+    pdl_wait();
+    const int e = tile_expert[blockIdx.y];
+    if (e < 0) return;
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Gs[BK][BN + 4];
+    __shared__ float Us[GLU ? BK : 1][BN + 4];
+    __shared__ int rows[BM];
+    const int slot0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    if (threadIdx.x < BM) {
+        const int pair = sorted_pair[slot0 + threadIdx.x];
+        rows[threadIdx.x] = pair < 0 ? -1 : (GLU ? pair / top : slot0 + (int)threadIdx.x);
+    }
+    __syncthreads();
+    const T* wg = Wg + (size_t)e * N * K;
+    const T* wu = GLU ? Wu + (size_t)e * N * K : nullptr;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float accg[2][4], accu[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) accg[i][j] = accu[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int i = threadIdx.x; i < BM * BK; i += 256) {
+            const int r = i / BK, c = i % BK;
+            const int gr = rows[r], gk = k0 + c;
+            As[c][r] = (gr >= 0 && gk < K) ? to_f<T>(A[(size_t)gr * K + gk]) : 0.f;
+        }
+        for (int i = threadIdx.x; i < BN * BK; i += 256) {
+            const int r = i / BK, c = i % BK;
+            const int gn = n0 + r, gk = k0 + c;
+            const bool in = gn < N && gk < K;
+            Gs[c][r] = in ? to_f<T>(wg[(size_t)gn * K + gk]) : 0.f;
+            if (GLU) Us[c][r] = in ? to_f<T>(wu[(size_t)gn * K + gk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[2], g[4], u[4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) a[i] = As[kk][ty * 2 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                g[j] = Gs[kk][tx * 4 + j];
+                u[j] = GLU ? Us[kk][tx * 4 + j] : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    accg[i][j] = fmaf(a[i], g[j], accg[i][j]);
+                    if (GLU) accu[i][j] = fmaf(a[i], u[j], accu[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = ty * 2 + i;
+        if (rows[r] < 0) continue;
+        const size_t orow = (size_t)(slot0 + r) * N;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tx * 4 + j;
+            if (gn >= N) continue;
+            if (GLU) {
+                const float g = fminf(accg[i][j], limit);
+                const float u = fminf(fmaxf(accu[i][j], -limit), limit);
+                ((T*)out_)[orow + gn] = from_f<T>(g * sigmoidf_(slope * g) * (u + shift));
+            } else {
+                ((float*)out_)[orow + gn] = accg[i][j];
+            }
+        }
+    }
+    pdl_trigger();
+}
+
+template <typename T>
+__global__ __launch_bounds__(256) void moe_combine_kernel(
+    const float* __restrict__ y, const int* __restrict__ pair_slot, const float* __restrict__ top_w,
+    const T* __restrict__ shared, const float* __restrict__ shared_gate, T* __restrict__ out, int width, int top) {
+    pdl_wait_and_trigger();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int slot = pair_slot[(size_t)t * top + k];
+            if (slot >= 0) acc = fmaf(top_w[(size_t)t * top + k], y[(size_t)slot * width + c], acc);
+        }
+        if (shared != nullptr)
+            acc = fmaf(shared_gate != nullptr ? shared_gate[t] : 1.0f, to_f<T>(shared[(size_t)t * width + c]), acc);
+        out[(size_t)t * width + c] = from_f<T>(acc);
+    }
+}
+
+template <typename T>
+__global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total,
+                               float slope, float limit, float shift) {
+    pdl_wait_and_trigger();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    const float g = fminf(to_f<T>(gu[t * 2 * inter + i]), limit);
+    const float u = fminf(fmaxf(to_f<T>(gu[t * 2 * inter + inter + i]), -limit), limit);
+    out[idx] = from_f<T>(g * sigmoidf_(slope * g) * (u + shift));
+}
+}  // namespace
+
+extern "C" int rlis_moe_tile_rows() { return BM; }
+
+// x [T, width] in the element type; w_router float32 [n_experts (+ 1 with shared_gate), width];
+// correction float32 [n_experts] or null; top_idx int32 [T, top]; top_w float32 [T, top]; shared_gate
+// float32 [T] or null.
+extern "C" int rlis_moe_route(const void* x, const float* w_router, const float* correction, int* top_idx,
+                              float* top_w, float* shared_gate, int n_tokens, int width, int n_experts, int top,
+                              float route_scale, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_experts <= 0 || top <= 0 || top > n_experts || n_experts > 4096) return RLIS_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(float);
+    if (dtype == RLIS_F32)
+        rlis_launch(moe_route_kernel<float>, n_tokens, 128, smem, stream, (const float*)x, w_router, correction, top_idx,
+                    top_w, shared_gate, width, n_experts, top, route_scale);
+    else if (dtype == RLIS_BF16)
+        rlis_launch(moe_route_kernel<bf16>, n_tokens, 128, smem, stream, (const bf16*)x, w_router, correction, top_idx,
+                    top_w, shared_gate, width, n_experts, top, route_scale);
+    else
+        return RLIS_ERR_UNSUPPORTED;
+    return RLIS_LAUNCH_CHECK();
+}
+
+extern "C" int rlis_moe_align(const int* top_idx, int* sorted_pair, int* pair_slot, int* tile_expert, int n_pairs,
+                              int n_experts, int max_tiles, cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    if (n_experts <= 0 || n_experts > 4096 || max_tiles < (n_pairs + BM - 1) / BM) return RLIS_ERR_UNSUPPORTED;
+    rlis_launch(moe_align_kernel, 1, 1024, (size_t)2 * n_experts * sizeof(int), stream, top_idx, sorted_pair, pair_slot,
+                tile_expert, n_pairs, n_experts, max_tiles);
+    return RLIS_LAUNCH_CHECK();
+}
+
+// glu != 0: A [T, K] rows of tokens, Wg and Wu [n_experts, N, K], out [max_tiles * tile, N] in the element type.
+// glu == 0: A [max_tiles * tile, K] rows of slots, Wg [n_experts, N, K], out float32 [max_tiles * tile, N].
+extern "C" int rlis_moe_gemm(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair,
+                             const int* tile_expert, int max_tiles, int top, int N, int K, int glu, float slope,
+                             float limit, float shift, int dtype, cudaStream_t stream) {
+    if (max_tiles <= 0 || N <= 0) return 0;
+    dim3 grid((N + BN - 1) / BN, max_tiles);
+    if (grid.y > 65535) return RLIS_ERR_UNSUPPORTED;
+#define RLIS_MOE(T, G) rlis_launch(moe_gemm_kernel<T, G>, grid, 256, 0, stream, (const T*)A, (const T*)Wg, (const T*)Wu, \
+                                   out, sorted_pair, tile_expert, top, N, K, slope, limit, shift)
+    if (dtype == RLIS_F32) { if (glu) RLIS_MOE(float, true); else RLIS_MOE(float, false); }
+    else if (dtype == RLIS_BF16) { if (glu) RLIS_MOE(bf16, true); else RLIS_MOE(bf16, false); }
+    else return RLIS_ERR_UNSUPPORTED;
+#undef RLIS_MOE
+    return RLIS_LAUNCH_CHECK();
+}
+
+extern "C" int rlis_moe_combine(const float* y, const int* pair_slot, const float* top_w, const void* shared,
+                                const float* shared_gate, void* out, int n_tokens, int width, int top, int dtype,
+                                cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (dtype == RLIS_F32)
+        rlis_launch(moe_combine_kernel<float>, n_tokens, 256, 0, stream, y, pair_slot, top_w, (const float*)shared,
+                    shared_gate, (float*)out, width, top);
+    else if (dtype == RLIS_BF16)
+        rlis_launch(moe_combine_kernel<bf16>, n_tokens, 256, 0, stream, y, pair_slot, top_w, (const bf16*)shared,
+                    shared_gate, (bf16*)out, width, top);
+    else
+        return RLIS_ERR_UNSUPPORTED;
+    return RLIS_LAUNCH_CHECK();
+}
+
+// out[t, i] = glu(gu[t, i], gu[t, inter + i]); limit +inf: no clipping.
+extern "C" int rlis_glu_act(const void* gu, void* out, int n_tokens, int inter, float slope, float limit, float shift,
+                            int dtype, cudaStream_t stream) {
+    const size_t total = (size_t)n_tokens * inter;
+    if (total == 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == RLIS_F32)
+        rlis_launch(glu_act_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, inter, total, slope, limit, shift);
+    else if (dtype == RLIS_BF16)
+        rlis_launch(glu_act_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, (bf16*)out, inter, total, slope, limit, shift);
+    else
+        return RLIS_ERR_UNSUPPORTED;
+    return RLIS_LAUNCH_CHECK();
+}

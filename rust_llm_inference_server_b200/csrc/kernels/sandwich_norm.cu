@@ -3,9 +3,11 @@
 //
 // post_norm_residual, one CTA a token:
 //   y      = sub[t, :] (+ bias)                                   sublayer result, widened
-//   resid += scale * (y / sqrt(mean(y^2) + eps) * w_post)         float32, in place
+//   resid += mult * scale * (y / sqrt(mean(y^2) + eps) * w_post)  float32, in place (mult a scalar, scale a vector)
 //   out    = resid / sqrt(mean(resid^2) + eps) * w_next           rounded once (only if w_next is given)
-// so the addition and the norm in front of the next sublayer cost one pass over the row.
+// so the addition and the norm in front of the next sublayer cost one pass over the row.  With `out` but
+// no w_next, out is the stream itself rounded to the activation type (for sublayers that read the stream
+// as it is); without `sub` nothing is added and only that copy is made.
 //
 // act_norm, one CTA a token: out = x / sqrt(mean(x^2) + eps) * w (* sigmoid(gate)), x float32 or the
 // activation type with a row stride of its own, gate in the activation type with a row stride.
@@ -20,7 +22,7 @@ template <typename T>
 __global__ __launch_bounds__(THREADS) void post_norm_residual_kernel(
     const T* __restrict__ sub, const float* __restrict__ bias, const float* __restrict__ w_post,
     const float* __restrict__ scale, float* __restrict__ resid, const float* __restrict__ w_next,
-    T* __restrict__ out, int hidden, float eps_post, float eps_next) {
+    T* __restrict__ out, int hidden, float eps_post, float eps_next, float mult) {
     pdl_wait_and_trigger();
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * hidden;
@@ -30,7 +32,7 @@ __global__ __launch_bounds__(THREADS) void post_norm_residual_kernel(
     for (int i = 0; i < MAX_PER_THREAD; ++i) {
         const int c = threadIdx.x + i * THREADS;
         v[i] = 0.f;
-        if (c < hidden) {
+        if (c < hidden && sub != nullptr) {
             v[i] = to_f<T>(sub[base + c]) + (bias != nullptr ? bias[c] : 0.f);
             ss = fmaf(v[i], v[i], ss);
         }
@@ -42,14 +44,26 @@ __global__ __launch_bounds__(THREADS) void post_norm_residual_kernel(
     for (int i = 0; i < MAX_PER_THREAD; ++i) {
         const int c = threadIdx.x + i * THREADS;
         if (c < hidden) {
-            const float normed = v[i] * r1 * w_post[c];
-            const float x = resid[base + c] + (scale != nullptr ? scale[c] * normed : normed);
-            resid[base + c] = x;
+            float x = resid[base + c];
+            if (sub != nullptr) {
+                const float normed = v[i] * r1 * w_post[c];
+                x += mult * (scale != nullptr ? scale[c] * normed : normed);
+                resid[base + c] = x;
+            }
             v[i] = x;
             ss2 = fmaf(x, x, ss2);
         }
     }
-    if (w_next == nullptr) return;
+    if (w_next == nullptr) {
+        if (out != nullptr) {
+#pragma unroll
+            for (int i = 0; i < MAX_PER_THREAD; ++i) {
+                const int c = threadIdx.x + i * THREADS;
+                if (c < hidden) out[base + c] = from_f<T>(v[i]);
+            }
+        }
+        return;
+    }
     ss2 = block_sum(ss2, scratch);
     const float r2 = 1.0f / sqrtf(ss2 / (float)hidden + eps_next);
 #pragma unroll
@@ -120,7 +134,7 @@ template <typename T, int NV>
 __global__ __launch_bounds__(THREADS) void post_norm_residual_vec_kernel(
     const T* __restrict__ sub, const float* __restrict__ bias, const float* __restrict__ w_post,
     const float* __restrict__ scale, float* __restrict__ resid, const float* __restrict__ w_next,
-    T* __restrict__ out, int hidden, float eps_post, float eps_next) {
+    T* __restrict__ out, int hidden, float eps_post, float eps_next, float mult) {
     pdl_wait_and_trigger();
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * hidden;
@@ -130,7 +144,7 @@ __global__ __launch_bounds__(THREADS) void post_norm_residual_vec_kernel(
     for (int i = 0; i < NV; ++i) {
         const int c = (threadIdx.x + i * THREADS) * 4;
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c < hidden) {
+        if (c < hidden && sub != nullptr) {
             v[i] = Quad<T>::load(sub + base + c);
             if (bias != nullptr) {
                 const float4 b = Quad<float>::load(bias + c);
@@ -147,20 +161,31 @@ __global__ __launch_bounds__(THREADS) void post_norm_residual_vec_kernel(
     for (int i = 0; i < NV; ++i) {
         const int c = (threadIdx.x + i * THREADS) * 4;
         if (c < hidden) {
-            const float4 w = Quad<float>::load(w_post + c);
-            const float4 s = scale != nullptr ? Quad<float>::load(scale + c) : make_float4(1.f, 1.f, 1.f, 1.f);
             float4 x = Quad<float>::load(resid + base + c);
-            const float n0 = v[i].x * r1 * w.x, n1 = v[i].y * r1 * w.y, n2 = v[i].z * r1 * w.z, n3 = v[i].w * r1 * w.w;
-            x.x += scale != nullptr ? s.x * n0 : n0;
-            x.y += scale != nullptr ? s.y * n1 : n1;
-            x.z += scale != nullptr ? s.z * n2 : n2;
-            x.w += scale != nullptr ? s.w * n3 : n3;
-            Quad<float>::store(resid + base + c, x);
+            if (sub != nullptr) {
+                const float4 w = Quad<float>::load(w_post + c);
+                const float4 s = scale != nullptr ? Quad<float>::load(scale + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+                const float n0 = v[i].x * r1 * w.x, n1 = v[i].y * r1 * w.y, n2 = v[i].z * r1 * w.z, n3 = v[i].w * r1 * w.w;
+                x.x += mult * (scale != nullptr ? s.x * n0 : n0);
+                x.y += mult * (scale != nullptr ? s.y * n1 : n1);
+                x.z += mult * (scale != nullptr ? s.z * n2 : n2);
+                x.w += mult * (scale != nullptr ? s.w * n3 : n3);
+                Quad<float>::store(resid + base + c, x);
+            }
             v[i] = x;
             ss2 = fmaf(x.x, x.x, ss2); ss2 = fmaf(x.y, x.y, ss2); ss2 = fmaf(x.z, x.z, ss2); ss2 = fmaf(x.w, x.w, ss2);
         }
     }
-    if (w_next == nullptr) return;
+    if (w_next == nullptr) {
+        if (out != nullptr) {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int c = (threadIdx.x + i * THREADS) * 4;
+                if (c < hidden) Quad<T>::store(out + base + c, v[i]);
+            }
+        }
+        return;
+    }
     ss2 = block_sum(ss2, scratch);
     const float r2 = 1.0f / sqrtf(ss2 / (float)hidden + eps_next);
 #pragma unroll
@@ -252,13 +277,13 @@ __global__ void bias_act_kernel(const T* __restrict__ x, const float* __restrict
 
 extern "C" int rlis_post_norm_residual(const void* sub, const float* bias, const float* w_post, const float* scale,
                                        float* resid, const float* w_next, void* out, int n_tokens, int hidden,
-                                       float eps_post, float eps_next, int dtype, cudaStream_t stream) {
+                                       float eps_post, float eps_next, float mult, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hidden <= 0 || hidden > THREADS * MAX_PER_THREAD) return RLIS_ERR_UNSUPPORTED;
     if (hidden % 4 == 0 && (dtype == RLIS_F32 || dtype == RLIS_BF16)) {
         const int nv = (hidden / 4 + THREADS - 1) / THREADS;
 #define RLIS_PNR(T, NV) rlis_launch(post_norm_residual_vec_kernel<T, NV>, n_tokens, THREADS, 0, stream, (const T*)sub, bias, \
-                                    w_post, scale, resid, w_next, (T*)out, hidden, eps_post, eps_next)
+                                    w_post, scale, resid, w_next, (T*)out, hidden, eps_post, eps_next, mult)
 #define RLIS_PNR_T(T) do { if (nv <= 1) RLIS_PNR(T, 1); else if (nv <= 2) RLIS_PNR(T, 2); else if (nv <= 4) RLIS_PNR(T, 4); \
                            else RLIS_PNR(T, 8); } while (0)
         if (dtype == RLIS_F32) RLIS_PNR_T(float); else RLIS_PNR_T(bf16);
@@ -268,10 +293,10 @@ extern "C" int rlis_post_norm_residual(const void* sub, const float* bias, const
     }
     if (dtype == RLIS_F32)
         rlis_launch(post_norm_residual_kernel<float>, n_tokens, THREADS, 0, stream, (const float*)sub, bias, w_post,
-                    scale, resid, w_next, (float*)out, hidden, eps_post, eps_next);
+                    scale, resid, w_next, (float*)out, hidden, eps_post, eps_next, mult);
     else if (dtype == RLIS_BF16)
         rlis_launch(post_norm_residual_kernel<bf16>, n_tokens, THREADS, 0, stream, (const bf16*)sub, bias, w_post,
-                    scale, resid, w_next, (bf16*)out, hidden, eps_post, eps_next);
+                    scale, resid, w_next, (bf16*)out, hidden, eps_post, eps_next, mult);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

@@ -71,6 +71,9 @@ class StepContext:
         self.wants_every_row = False              # ... and they are all the step's rows, in order
         self._views = None
         self._token_region = None
+        # what a part leaves for parts that run later in the same step (tensors that concern this step's
+        # tokens only: nothing here outlives the step)
+        self.carry: dict = {}
 
     def buffer(self, name: str, shape, dtype) -> torch.Tensor:
         return self._runner.workspace(name, shape, dtype)

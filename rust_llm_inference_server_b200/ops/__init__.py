@@ -218,29 +218,37 @@ def per_head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torc
     return out
 
 
-def post_norm_residual(sub: torch.Tensor, resid: torch.Tensor, w_post: torch.Tensor, eps_post: float,
+def post_norm_residual(sub: torch.Tensor | None, resid: torch.Tensor, w_post: torch.Tensor | None, eps_post: float,
                        scale: torch.Tensor | None = None, bias: torch.Tensor | None = None,
                        w_next: torch.Tensor | None = None, eps_next: float = 0.0,
-                       out: torch.Tensor | None = None):
-    """resid += scale * rmsnorm(sub + bias) * w_post, all in float32 and in place; with `w_next` also
-    out = rmsnorm(resid) * w_next (the norm in front of the next sublayer), rounded once to sub's type.
+                       out: torch.Tensor | None = None, mult: float = 1.0):
+    """resid += mult * scale * rmsnorm(sub + bias) * w_post, all in float32 and in place (`mult` a number,
+    `scale` a vector); with `w_next` also out = rmsnorm(resid) * w_next (the norm in front of the next
+    sublayer), rounded once to sub's type.  `out` without `w_next`: out = resid rounded to out's type, for a
+    sublayer that reads the stream as it is; `sub` None: nothing is added and only that copy is made.
     sub [T, H] in the activation type; resid float32 [T, H]; the vectors float32 [H]."""
     T, H = resid.shape
     _req(resid, "resid", torch.float32)
-    _req(sub, "sub", None, (T, H))
-    _req(w_post, "w_post", torch.float32, (H,))
+    if sub is not None:
+        _req(sub, "sub", None, (T, H))
+        _req(w_post, "w_post", torch.float32, (H,))
+    elif out is None or w_next is not None:
+        raise KernelError("post_norm_residual: without a sublayer result only the copy of the stream is made")
     for v, nm in ((scale, "scale"), (bias, "bias"), (w_next, "w_next")):
         if v is not None:
             _req(v, nm, torch.float32, (H,))
-    if w_next is not None:
-        _req(out, "out", sub.dtype, (T, H))
-    check(lib().rlis_post_norm_residual(sub.data_ptr(), bias.data_ptr() if bias is not None else None,
-                                        w_post.data_ptr(), scale.data_ptr() if scale is not None else None,
+    if w_next is not None or out is not None:
+        _req(out, "out", sub.dtype if sub is not None else None, (T, H))
+    dtype = sub.dtype if sub is not None else out.dtype
+    check(lib().rlis_post_norm_residual(sub.data_ptr() if sub is not None else None,
+                                        bias.data_ptr() if bias is not None else None,
+                                        w_post.data_ptr() if sub is not None else None,
+                                        scale.data_ptr() if scale is not None else None,
                                         resid.data_ptr(), w_next.data_ptr() if w_next is not None else None,
-                                        out.data_ptr() if w_next is not None else None, T, H, float(eps_post),
-                                        float(eps_next), _code(sub.dtype), _stream()), "post_norm_residual")
-    _count("post_norm_residual" + (".next" if w_next is not None else ""))
-    return out if w_next is not None else None
+                                        out.data_ptr() if out is not None else None, T, H, float(eps_post),
+                                        float(eps_next), float(mult), _code(dtype), _stream()), "post_norm_residual")
+    _count("post_norm_residual" + (".next" if w_next is not None else ".copy" if out is not None else ""))
+    return out
 
 
 def act_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -937,6 +945,191 @@ def attention(q, k_cache, v_cache, out, step, group: int, n_heads: int, n_kv_hea
         rows = step.dec_rows                          # the single tokens only
     return attention_generic(q, k_cache, v_cache, out, step.seq_of_token, step.positions, tables,
                              n_heads, n_kv_heads, head_dim, page_size, scale, window, token_rows=rows)
+
+
+def glu_act(gate_up: torch.Tensor, out: torch.Tensor, slope: float = 1.0, limit: float | None = None,
+            up_shift: float = 0.0) -> torch.Tensor:
+    """out[t, i] = g sigmoid(slope g) (u + up_shift) with g = gate_up[t, i] and u = gate_up[t, I + i], both in
+    float32; with a `limit`, g is cut at limit from above and u clipped to [-limit, limit] first."""
+    T, I2 = gate_up.shape
+    if I2 % 2:
+        raise KernelError(f"glu_act: the stacked gate|up width must be even, got {I2}")
+    _req(gate_up, "gate_up")
+    _req(out, "out", gate_up.dtype, (T, I2 // 2))
+    check(lib().rlis_glu_act(gate_up.data_ptr(), out.data_ptr(), T, I2 // 2, float(slope),
+                             float("inf") if limit is None else float(limit), float(up_shift), _code(out.dtype),
+                             _stream()), "glu_act")
+    _count("glu_act")
+    return out
+
+
+def qk_norm_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w, k_w, eps: float, v_other, lam: float,
+                  q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slots, n_heads: int,
+                  n_kv_heads: int, dim: int, v_dim: int, page_size: int) -> torch.Tensor:
+    """From the rows of a stacked projection `proj` [T, N] (queries at column q_off, keys at k_off, values
+    at v_off): q_out [T, nh dim] = per-head rmsnorm(q) * q_w, and at `slots` of the paged caches the keys
+    rmsnorm(k) * k_w and the values, mixed as (1 - lam) v + lam v_other where `v_other` (a [T, nkv v_dim]
+    column slice of another projection's rows) is given.  q_w, k_w float32 [dim] or None (no norm); slots
+    None: nothing is stored.  Statistics and the mixing are float32."""
+    T, N = proj.shape
+    _req(proj, "proj")
+    _req(q_out, "q_out", proj.dtype, (T, n_heads * dim))
+    for w, nm in ((q_w, "q_w"), (k_w, "k_w")):
+        if w is not None:
+            _req(w, nm, torch.float32, (dim,))
+    if v_off + n_kv_heads * v_dim > N or k_off + n_kv_heads * dim > N or q_off + n_heads * dim > N:
+        raise KernelError("qk_norm_store: the column offsets reach beyond the projection's rows")
+    if slots is not None:
+        _req(slots, "slots", torch.int32, (T,))
+        _req(k_cache, "k_cache", proj.dtype, (None, n_kv_heads, page_size, dim))
+        _req(v_cache, "v_cache", proj.dtype, (None, n_kv_heads, page_size, v_dim))
+    vo, vo_stride = None, 0
+    if v_other is not None:
+        if (v_other.dtype != proj.dtype or tuple(v_other.shape) != (T, n_kv_heads * v_dim) or v_other.stride(1) != 1
+                or not v_other.is_cuda):
+            raise KernelError("qk_norm_store: the other layer's values must be [T, nkv v_dim] rows with unit stride")
+        vo, vo_stride = v_other.data_ptr(), v_other.stride(0)
+    check(lib().rlis_qk_norm_store(proj.data_ptr(), N, int(q_off), int(k_off), int(v_off),
+                                   q_w.data_ptr() if q_w is not None else None,
+                                   k_w.data_ptr() if k_w is not None else None, float(eps), vo, vo_stride, float(lam),
+                                   q_out.data_ptr(), k_cache.data_ptr() if slots is not None else None,
+                                   v_cache.data_ptr() if slots is not None else None,
+                                   slots.data_ptr() if slots is not None else None, T, n_heads, n_kv_heads, dim, v_dim,
+                                   page_size, _code(proj.dtype), _stream()), "qk_norm_store")
+    _count("qk_norm_store" + (".mix" if v_other is not None else ""))
+    return q_out
+
+
+def biased_attention_takes_mma(dtype, n_heads: int, n_kv_heads: int, dim: int, v_dim: int) -> bool:
+    """Whether the tensor-core kernels for attention with a bias by distance exist for these sizes."""
+    return False
+
+
+def biased_decode_pieces(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
+    return 1
+
+
+def attention_biased(q, k_cache, v_cache, out, bias, gate, step, group: int, n_heads: int, n_kv_heads: int,
+                     dim: int, v_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Causal grouped-query attention of every token of the step over its request's cached keys:
+    score = scale * q . k + bias[min(distance, len(bias) - 1), head]; a head's result is multiplied by
+    sigmoid(gate[t, head]).  q [T, nh dim]; k_cache [pages, nkv, page_size, dim]; v_cache [pages, nkv,
+    page_size, v_dim]; out [T, nh v_dim]; bias float32 [n_dist, nh] or None; gate [T, nh] (a column slice
+    of wider rows) or None."""
+    T = q.shape[0]
+    _req(q, "q", None, (T, n_heads * dim))
+    _req(out, "out", q.dtype, (T, n_heads * v_dim))
+    _req(k_cache, "k_cache", q.dtype, (None, n_kv_heads, page_size, dim))
+    _req(v_cache, "v_cache", q.dtype, (None, n_kv_heads, page_size, v_dim))
+    n_dist = 0
+    if bias is not None:
+        _req(bias, "bias", torch.float32, (None, n_heads))
+        n_dist = bias.shape[0]
+    gp, gs = None, 0
+    if gate is not None:
+        if gate.dtype != q.dtype or tuple(gate.shape) != (T, n_heads) or gate.stride(1) != 1 or not gate.is_cuda:
+            raise KernelError("attention_biased: the gate must be [T, nh] rows with unit stride in q's type")
+        gp, gs = gate.data_ptr(), gate.stride(0)
+    tables = step.block_tables[group]
+    check(lib().rlis_attention_bias(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                    bias.data_ptr() if bias is not None else None, n_dist, gp, gs,
+                                    step.seq_of_token.data_ptr(), step.positions.data_ptr(), tables.data_ptr(), None,
+                                    tables.shape[1], T, n_heads, n_kv_heads, dim, v_dim, page_size, float(scale),
+                                    int(window), _code(q.dtype), _stream()), "attention_bias")
+    _count("attention_bias")
+    return out
+
+
+class MoePlan:
+    """Where a step's (token, choice) pairs go: the chosen experts and weights, the pairs sorted by expert
+    into slots in tiles of `tile` rows, and the shared expert's gate; all on the device."""
+
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+@functools.lru_cache(maxsize=None)
+def moe_tile_rows() -> int:
+    return int(lib().rlis_moe_tile_rows())
+
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: int, top: int, route_scale: float,
+              shared_gate: bool, step) -> MoePlan:
+    """Scores s = sigmoid(w_router x) in float32; the `top` experts with the largest s + correction; weights
+    s * route_scale.  w_router float32 [n_experts (+ 1), width]: with `shared_gate` its last row is the logit
+    of the shared expert's gate.  Then the pairs are sorted by expert on the device."""
+    T, W = x.shape
+    _req(x, "x")
+    rows = n_experts + (1 if shared_gate else 0)
+    _req(w_router, "w_router", torch.float32, (rows, W))
+    if correction is not None:
+        _req(correction, "correction", torch.float32, (n_experts,))
+    pairs = T * top
+    tile = moe_tile_rows()
+    max_tiles = min(pairs, n_experts) + pairs // tile      # every expert in use ends in at most one partial tile
+    ints = step.buffer("moe_ints", (2 * pairs + max_tiles * tile + max_tiles,), torch.int32)
+    flts = step.buffer("moe_floats", (pairs + T,), torch.float32)
+    top_idx, pair_slot = ints[:pairs], ints[pairs:2 * pairs]
+    sorted_pair = ints[2 * pairs:2 * pairs + max_tiles * tile]
+    tile_expert = ints[2 * pairs + max_tiles * tile:]
+    top_w, gate = flts[:pairs], flts[pairs:]
+    check(lib().rlis_moe_route(x.data_ptr(), w_router.data_ptr(), correction.data_ptr() if correction is not None else None,
+                               top_idx.data_ptr(), top_w.data_ptr(), gate.data_ptr() if shared_gate else None, T, W,
+                               n_experts, top, float(route_scale), _code(x.dtype), _stream()), "moe_route")
+    _count("moe_route")
+    check(lib().rlis_moe_align(top_idx.data_ptr(), sorted_pair.data_ptr(), pair_slot.data_ptr(), tile_expert.data_ptr(),
+                               pairs, n_experts, max_tiles, _stream()), "moe_align")
+    _count("moe_align")
+    return MoePlan(n_tokens=T, top=top, n_experts=n_experts, tile=tile, max_tiles=max_tiles, top_idx=top_idx,
+                   top_w=top_w, pair_slot=pair_slot, sorted_pair=sorted_pair, tile_expert=tile_expert,
+                   shared_gate=gate if shared_gate else None)
+
+
+def moe_up(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, plan: MoePlan, slope: float, limit: float,
+           up_shift: float, step) -> torch.Tensor:
+    """act[slot, :] = glu(w_gate[e] x_t, w_up[e] x_t) for the token t and expert e of every slot (see `glu_act`);
+    w_gate, w_up [experts, I, width]; returns [slots, I] in x's type."""
+    T, W = x.shape
+    E, I, _ = w_gate.shape
+    _req(x, "x")
+    _req(w_gate, "w_gate", x.dtype, (plan.n_experts, I, W))
+    _req(w_up, "w_up", x.dtype, (plan.n_experts, I, W))
+    act = step.buffer("moe_act", (plan.max_tiles * plan.tile, I), x.dtype)
+    check(lib().rlis_moe_gemm(x.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), act.data_ptr(),
+                              plan.sorted_pair.data_ptr(), plan.tile_expert.data_ptr(), plan.max_tiles, plan.top, I, W,
+                              1, float(slope), float(limit), float(up_shift), _code(x.dtype), _stream()), "moe_up")
+    _count("moe_gemm.glu")
+    return act
+
+
+def moe_down(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan, step) -> torch.Tensor:
+    """y[slot, :] = w_down[e] act[slot, :] in float32; w_down [experts, width, I]."""
+    S, I = act.shape
+    E, W, _ = w_down.shape
+    _req(act, "act", None, (plan.max_tiles * plan.tile, I))
+    _req(w_down, "w_down", act.dtype, (plan.n_experts, W, I))
+    y = step.buffer("moe_y", (S, W), torch.float32)
+    check(lib().rlis_moe_gemm(act.data_ptr(), w_down.data_ptr(), None, y.data_ptr(), plan.sorted_pair.data_ptr(),
+                              plan.tile_expert.data_ptr(), plan.max_tiles, plan.top, W, I, 0, 1.0, 0.0, 0.0,
+                              _code(act.dtype), _stream()), "moe_down")
+    _count("moe_gemm.down")
+    return y
+
+
+def moe_combine(y: torch.Tensor, plan: MoePlan, shared, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum over a token's choices of weight * y[slot] (+ gate[t] * shared[t], gate 1 without one),
+    summed in float32 in the order of the choices."""
+    T, W = out.shape
+    _req(y, "y", torch.float32, (None, W))
+    _req(out, "out")
+    if shared is not None:
+        _req(shared, "shared", out.dtype, (T, W))
+    check(lib().rlis_moe_combine(y.data_ptr(), plan.pair_slot.data_ptr(), plan.top_w.data_ptr(),
+                                 shared.data_ptr() if shared is not None else None,
+                                 plan.shared_gate.data_ptr() if plan.shared_gate is not None else None, out.data_ptr(),
+                                 T, W, plan.top, _code(out.dtype), _stream()), "moe_combine")
+    _count("moe_combine")
+    return out
 
 
 def sample_rows(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -59,11 +59,13 @@ class KVCacheSpec:
     """What a mixer keeps per token: keys and values of `n_kv_heads` heads of `head_dim`, of all
     earlier tokens (window None) or of the last `window` tokens.  `values=False`: one row per head
     and token only (a mixer that derives keys and values from the same stored row); the slot's
-    storage then has no second plane and `LayerCache.v` is None."""
+    storage then has no second plane and `LayerCache.v` is None.  `v_head_dim`: the width of a value
+    row where it differs from a key row's (None: the same); keys and values then live in two pools."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     values: bool = True
+    v_head_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -77,7 +79,8 @@ class StateSpec:
 class LayerCache:
     """One cache slot's device storage as a mixer sees it."""
     k: torch.Tensor                  # [pages, n_kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor]        # None for a slot that keeps one row per token (KVCacheSpec.values False)
+    v: Optional[torch.Tensor]        # [pages, n_kv_heads, page_size, v_head_dim or head_dim]; None for a slot
+                                     # that keeps one row per token (KVCacheSpec.values False)
     group: int                       # index into the step's block tables and slot lists
     page_size: int
 

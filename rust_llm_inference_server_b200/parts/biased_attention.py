@@ -1,0 +1,151 @@
+"""Causal grouped-query attention without rotation: per-head RMS norms of queries and keys, a learned
+bias by distance, values of their own width that a layer may mix with another layer's, and a gate on
+every head's output."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..ops.profile import span
+from .base import KVCacheSpec, Mixer, register_mixer
+
+
+def log_bucket(n: int, rows: int, far: float) -> int:
+    """The table row of a key n positions back (see `parts.spec.DistanceBiasSpec`)."""
+    half = rows // 2
+    if n < half:
+        return n
+    return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+
+
+def bias_by_distance(table: torch.Tensor, far: float) -> torch.Tensor:
+    """float32 [n_dist, heads]: the bias of a key n positions back, for every n up to the first distance
+    from which all share the table's last row (the kernels clamp larger distances to the last entry)."""
+    rows = table.shape[0]
+    if rows < 2 or not far > rows // 2:
+        raise ValueError(f"a distance-bias table of {rows} rows does not reach up to distance {far}")
+    buckets, n = [], 0
+    while True:
+        b = log_bucket(n, rows, far)
+        buckets.append(b)
+        if b == rows - 1 and n >= far:
+            break
+        n += 1
+    return table.float()[torch.tensor(buckets, dtype=torch.long, device=table.device)].contiguous()
+
+
+class BiasedAttention(Mixer):
+    """One stacked product makes q | k | v | gate logits; one kernel norms q and k per head, mixes the
+    values where the layer does and stores keys and values in the paged cache; attention adds the bias by
+    distance to every score and applies the gate to every head's result; then the output projection.
+
+    The layer with `value_source` leaves its values (a view of its projection's rows) in `step.carry`
+    for the layers that mix them in: they concern the same tokens of the same step, so nothing has to be
+    kept between steps.  Norms, scores, softmax, value sums, mixing and gate are float32."""
+
+    graph_safe = True
+
+    CARRY_KEY = "biased_attention.values"
+
+    def __init__(self, spec, dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        if spec.n_heads % spec.n_kv_heads:
+            raise ValueError(f"{spec.n_heads} query heads are not a multiple of {spec.n_kv_heads} key/value heads")
+        if spec.dim > 256 or spec.v_dim > 256:
+            raise ValueError(f"attention kernels take head sizes up to 256, got {spec.dim} / {spec.v_dim}")
+        self.eps = float(np.float32(spec.eps))
+        self.scale = float(spec.scale)
+        self.window = int(spec.window) if spec.window else 0
+        self.q_off = 0
+        self.k_off = spec.n_heads * spec.dim
+        self.v_off = self.k_off + spec.n_kv_heads * spec.dim
+        self.g_off = self.v_off + spec.n_kv_heads * spec.v_dim
+        self.lam = 0.0
+        self.bias = self.q_w = self.k_w = None
+
+    def tensors(self) -> dict:
+        s = self.spec
+        out = {s.q_proj: (s.n_heads * s.dim, s.hidden), s.k_proj: (s.n_kv_heads * s.dim, s.hidden),
+               s.v_proj: (s.n_kv_heads * s.v_dim, s.hidden), s.o_proj: (s.hidden, s.n_heads * s.v_dim)}
+        if s.q_norm is not None:
+            out[s.q_norm] = (s.dim,)
+        if s.k_norm is not None:
+            out[s.k_norm] = (s.dim,)
+        if s.bias is not None:
+            out[s.bias.table] = (s.bias.rows, s.n_heads)
+        if s.head_gate is not None:
+            out[s.head_gate] = (s.n_heads, s.hidden)
+        if s.value_mix is not None:
+            out[s.value_mix] = ()
+        for name in s.unused:
+            out[name] = ()
+        return out
+
+    def load(self, src) -> None:
+        s = self.spec
+        parts = [src.get(s.q_proj), src.get(s.k_proj), src.get(s.v_proj)]
+        if s.head_gate is not None:
+            parts.append(src.get(s.head_gate))
+        w = torch.cat(parts, dim=0)
+        pad = -w.shape[0] % 8             # rows of the stacked projection stay 16-byte multiples
+        if pad:
+            w = torch.cat([w, w.new_zeros((pad, w.shape[1]))], dim=0)
+        self.w_in = w.contiguous()
+        self.w_o = src.get(s.o_proj).contiguous()
+        self.q_w = src.get(s.q_norm, "vector").contiguous() if s.q_norm is not None else None
+        self.k_w = src.get(s.k_norm, "vector").contiguous() if s.k_norm is not None else None
+        if s.bias is not None:
+            self.bias = bias_by_distance(src.get(s.bias.table, "vector"), float(s.bias.far))
+        if s.value_mix is not None:
+            self.lam = float(src.get(s.value_mix, "vector").reshape(-1)[0].item())
+
+    def cache_spec(self):
+        s = self.spec
+        return KVCacheSpec(s.n_kv_heads, s.dim, s.window, v_head_dim=s.v_dim if s.v_dim != s.dim else None)
+
+    def _fast(self) -> bool:
+        s = self.spec
+        return ops.biased_attention_takes_mma(self.dtype, s.n_heads, s.n_kv_heads, s.dim, s.v_dim)
+
+    @property
+    def prefill_tile(self):
+        return ops.prefill_tile() if self._fast() else None
+
+    def launch_variant(self, step):
+        if not step.n_decode or not self._fast():
+            return None
+        s = self.spec
+        return ops.biased_decode_pieces(step.n_decode, s.n_kv_heads, step.max_decode_ctx)
+
+    def forward(self, x, step, cache, state, writes_cache=True):
+        s = self.spec
+        T = x.shape[0]
+        with span("q|k|v|gate proj"):
+            proj = ops.linear(x, self.w_in)
+        other = None
+        if s.value_source:
+            step.carry[self.CARRY_KEY] = proj[:, self.v_off:self.v_off + s.n_kv_heads * s.v_dim]
+        elif s.value_mix is not None:
+            other = step.carry.get(self.CARRY_KEY)
+            if other is None:
+                raise RuntimeError("a layer mixes in another layer's values, and no layer of this step has left any")
+        q = step.buffer("attn_q", (T, s.n_heads * s.dim), self.dtype)
+        with span("q, k norms + value mix + kv write"):
+            ops.qk_norm_store(proj, self.q_off, self.k_off, self.v_off, self.q_w, self.k_w, self.eps, other, self.lam, q,
+                              cache.k, cache.v, step.slots[cache.group] if writes_cache else None, s.n_heads,
+                              s.n_kv_heads, s.dim, s.v_dim, cache.page_size)
+        o = step.buffer("attn_o", (T, s.n_heads * s.v_dim), self.dtype)
+        gate = proj[:, self.g_off:self.g_off + s.n_heads] if s.head_gate is not None else None
+        with span("attention"):
+            ops.attention_biased(q, cache.k, cache.v, o, self.bias, gate, step, cache.group, s.n_heads, s.n_kv_heads,
+                                 s.dim, s.v_dim, cache.page_size, self.scale, self.window)
+        with span("o proj"):
+            return ops.linear(o, self.w_o)
+
+
+register_mixer("biased_attention", BiasedAttention)

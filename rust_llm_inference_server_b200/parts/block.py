@@ -13,6 +13,8 @@ blocks: the model names the next block, and `entry_sink` answers for its first n
 
 from __future__ import annotations
 
+import torch
+
 from .. import ops
 from .base import (Part, build_feed_forward, build_mixer, build_norm, register_arrangement)
 
@@ -106,6 +108,68 @@ class SandwichBlock:
                           bias=self.feed_forward.b_down if defer else None)
 
 
+class OutNormBlock:
+    """x += m * norm1(mixer(x)); x += m * norm2(feed_forward(x)), the second line only when the layer has a
+    feed-forward.  The sublayers read the stream as it is, and only their results are normed.  The stream
+    and the norms are float32: one kernel norms a result, adds it to the stream and leaves the stream,
+    rounded to the compute type, for the sublayer that follows (in float32 that sublayer reads the stream
+    itself).  A block returns no pending delta, and hands the next block of its kind the rounded stream."""
+
+    def __init__(self, spec, dtype, device):
+        self.dtype = dtype
+        self.mult = float(spec.residual_mult)
+        self.hidden = spec.norm1.dim
+        self.mixer = build_mixer(spec.mixer, dtype, device)
+        self.norm1 = build_norm(spec.norm1, dtype, device)
+        self.feed_forward = build_feed_forward(spec.feed_forward, dtype, device) if spec.feed_forward is not None else None
+        self.norm2 = build_norm(spec.norm2, dtype, device) if self.feed_forward is not None else None
+        for n in (self.norm1, self.norm2):
+            if n is not None and not hasattr(n, "weight"):
+                raise ValueError("the outnorm arrangement takes norms that are a weight and an eps (RMSNorm)")
+
+    chains_norms = True      # `forward` takes `next_block`
+
+    def entry_sink(self, resid, step):
+        return None
+
+    def parts(self):
+        return tuple(p for p in (self.mixer, self.norm1, self.feed_forward, self.norm2) if p is not None)
+
+    def _stream(self, resid, step):
+        """The stream as a sublayer reads it."""
+        if self.dtype == torch.float32:
+            return resid
+        h = step.buffer("stream_copy", (resid.shape[0], self.hidden), self.dtype)
+        return ops.post_norm_residual(None, resid, None, 0.0, out=h)
+
+    def _join(self, sub, norm, resid, step, wanted: bool):
+        """resid += m * norm(sub); returns the stream for the next sublayer if one is `wanted`."""
+        if not wanted or self.dtype == torch.float32:
+            ops.post_norm_residual(sub, resid, norm.weight, norm.eps, mult=self.mult)
+            return resid if wanted else None
+        h = step.buffer("stream_copy", (resid.shape[0], self.hidden), self.dtype)
+        return ops.post_norm_residual(sub, resid, norm.weight, norm.eps, mult=self.mult, out=h)
+
+    def forward(self, resid, pending, step, cache, state, writes_cache=True, next_block=None):
+        h = pending.x if isinstance(pending, StreamRows) else self._stream(resid, step)
+        a = self.mixer.forward(h, step, cache, state, writes_cache)
+        chained = isinstance(next_block, OutNormBlock) and next_block.dtype == self.dtype
+        if self.feed_forward is None:
+            h = self._join(a, self.norm1, resid, step, chained)
+        else:
+            h = self._join(a, self.norm1, resid, step, True)
+            f = self.feed_forward.forward(h, step)
+            h = self._join(f, self.norm2, resid, step, chained)
+        return resid, (StreamRows(h) if chained else None)
+
+
+class StreamRows:
+    """What an outnorm block hands the next one: `x`, the (complete) residual stream in the compute type."""
+
+    def __init__(self, x):
+        self.x = x
+
+
 class NormedRows:
     """What a block hands the next one when it has already normed the stream for it: `x`, the next
     block's first norm applied to the (complete) residual stream."""
@@ -135,3 +199,4 @@ class _BlockTensors(Part):
 
 register_arrangement("prenorm", PreNormBlock)
 register_arrangement("sandwich", SandwichBlock)
+register_arrangement("outnorm", OutNormBlock)

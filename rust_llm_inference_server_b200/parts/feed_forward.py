@@ -21,6 +21,10 @@ class SwiGLU(FeedForward):
         self.dtype = dtype
         self.w_gate_up = None
         self.w_down = None
+        # the plain form silu(g) * u has kernels that gate inside a product; other slopes, a clipping
+        # limit or a shifted linear branch go through the gating kernel that takes them as parameters
+        self.plain = (float(getattr(spec, "slope", 1.0)) == 1.0 and getattr(spec, "limit", None) is None
+                      and float(getattr(spec, "up_shift", 0.0)) == 0.0)
 
     def tensors(self) -> dict:
         s = self.spec
@@ -30,7 +34,7 @@ class SwiGLU(FeedForward):
     def load(self, src) -> None:
         s = self.spec
         g, u = src.get(s.gate_proj), src.get(s.up_proj)
-        self.interleave = 4 if s.intermediate % 4 == 0 else 0
+        self.interleave = 4 if s.intermediate % 4 == 0 and self.plain else 0
         if self.interleave:
             self.w_gate_up = torch.stack([g.view(-1, 4, s.hidden), u.view(-1, 4, s.hidden)], dim=1) \
                 .reshape(2 * s.intermediate, s.hidden).contiguous()
@@ -39,9 +43,18 @@ class SwiGLU(FeedForward):
         self.w_down = src.get(s.down_proj).contiguous()
 
     def fuses_norms(self, step) -> bool:
-        return ops.fuses_norms(step.n_tokens, self.dtype, self.spec.hidden, self.spec.intermediate)
+        return self.plain and ops.fuses_norms(step.n_tokens, self.dtype, self.spec.hidden, self.spec.intermediate)
 
     def forward(self, x, step, sink=None):
+        if not self.plain:
+            s = self.spec
+            with span("mlp gate+up"):
+                gu = ops.linear(x, self.w_gate_up)
+            with span("clipped gating"):
+                act = step.buffer("ffn_act", (x.shape[0], s.intermediate), self.dtype)
+                ops.glu_act(gu, act, s.slope, s.limit, s.up_shift)
+            with span("mlp down proj"):
+                return ops.linear(act, self.w_down)
         fusable = self.dtype == torch.bfloat16 and self.interleave == 4 and self.spec.hidden % 8 == 0
         with span("mlp gate+up, silu*up"):
             if fusable and x.shape[0] <= ops.STREAM_GEMM_ROWS:

@@ -1,0 +1,75 @@
+"""A feed-forward that routes every token to a few of many small gated feed-forwards, beside an optional
+shared one that every token runs through."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops.profile import span
+from .base import FeedForward, build_feed_forward, register_feed_forward
+
+
+class RoutedFF(FeedForward):
+    """Router scores in float32 from float32 copies of the router matrix (and of the shared expert's
+    gate row, which rides along as one more row); choice, weights and the sort of (token, choice) pairs
+    by expert happen on the device, so launches depend on the step's shape only.  The experts' matrices
+    are stacked [expert, out, in] at load time."""
+
+    graph_safe = True
+
+    def __init__(self, spec, dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        self.limit = float("inf") if spec.limit is None else float(spec.limit)
+        self.shared = build_feed_forward(spec.shared, dtype, device) if spec.shared is not None else None
+        if spec.shared_gate is not None and self.shared is None:
+            raise ValueError("a gate on the shared expert, and no shared expert")
+
+    def _names(self, pattern: str):
+        return [pattern.format(e=e) for e in range(self.spec.n_experts)]
+
+    def tensors(self) -> dict:
+        s = self.spec
+        out = {s.router: (s.n_experts, s.hidden)}
+        if s.correction is not None:
+            out[s.correction] = (s.n_experts,)
+        for n in self._names(s.gate_proj) + self._names(s.up_proj):
+            out[n] = (s.intermediate, s.hidden)
+        for n in self._names(s.down_proj):
+            out[n] = (s.hidden, s.intermediate)
+        if self.shared is not None:
+            out.update(self.shared.tensors())
+        if s.shared_gate is not None:
+            out[s.shared_gate] = (1, s.hidden)
+        return out
+
+    def load(self, src) -> None:
+        s = self.spec
+        rows = [src.get(s.router, "vector")]
+        if s.shared_gate is not None:
+            rows.append(src.get(s.shared_gate, "vector"))
+        self.w_router = torch.cat(rows, dim=0).contiguous()              # float32 [experts (+ 1), hidden]
+        self.correction = src.get(s.correction, "vector").contiguous() if s.correction is not None else None
+        self.w_gate = torch.stack([src.get(n) for n in self._names(s.gate_proj)]).contiguous()
+        self.w_up = torch.stack([src.get(n) for n in self._names(s.up_proj)]).contiguous()
+        self.w_down = torch.stack([src.get(n) for n in self._names(s.down_proj)]).contiguous()
+        if self.shared is not None:
+            self.shared.load(src)
+
+    def forward(self, x, step):
+        s = self.spec
+        T = x.shape[0]
+        with span("router"):
+            plan = ops.moe_route(x, self.w_router, self.correction, s.n_experts, s.top, s.route_scale,
+                                 s.shared_gate is not None, step)
+        y_shared = self.shared.forward(x, step) if self.shared is not None else None
+        with span("experts"):
+            act = ops.moe_up(x, self.w_gate, self.w_up, plan, s.slope, self.limit, s.up_shift, step)
+            y = ops.moe_down(act, self.w_down, plan, step)
+        out = step.buffer("ffn_out", (T, s.hidden), self.dtype)
+        with span("combine"):
+            return ops.moe_combine(y, plan, y_shared, out)
+
+
+register_feed_forward("routed_ff", RoutedFF)

@@ -75,6 +75,50 @@ class GQAAttentionSpec:
 
 
 @dataclass(frozen=True)
+class DistanceBiasSpec:
+    """A learned bias added to a score by how far back its key lies: row bucket(n) of `table`
+    (rows, n_heads) for a key n positions before the query.  With half = rows // 2: bucket(n) = n below
+    half; from there on the rows are spaced evenly in ln(n) up to `far`, bucket(n) = min(rows - 1,
+    half + floor(ln(n / half) / ln(far / half) * (rows - half)))."""
+    table: str                       # (rows, n_heads)
+    rows: Optional[int]              # None: as many as the checkpoint's tensor has
+    far: float
+    kind: str = "log_buckets"
+
+
+@dataclass(frozen=True)
+class BiasedAttentionSpec:
+    """Causal grouped-query attention without rotation: queries and keys are RMS-normed per head
+    (weights `q_norm`, `k_norm` of size `dim`, shared by the heads; None: no norm), score = scale *
+    q . k + bias by distance (`bias`, None: none), values have a width of their own (`v_dim`).
+    `value_mix` names a scalar lambda: the layer caches and uses (1 - lambda) v + lambda v_src, v_src
+    being the values that the layer with `value_source` made of the same token (that layer's own values
+    stay unmixed).  `head_gate` (n_heads, hidden): head h's output is multiplied by sigmoid of row h
+    applied to the mixer's input."""
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    dim: int
+    v_dim: int
+    scale: float
+    eps: float
+    q_proj: str                      # (n_heads * dim, hidden)
+    k_proj: str                      # (n_kv_heads * dim, hidden)
+    v_proj: str                      # (n_kv_heads * v_dim, hidden)
+    o_proj: str                      # (hidden, n_heads * v_dim)
+    q_norm: Optional[str] = None     # (dim,)
+    k_norm: Optional[str] = None     # (dim,)
+    bias: Any = None                 # a DistanceBiasSpec
+    head_gate: Optional[str] = None  # (n_heads, hidden)
+    value_mix: Optional[str] = None  # scalar tensor
+    value_source: bool = False
+    # a tensor of the checkpoint that this layer does not read (a mixing weight on the source layer)
+    unused: tuple = ()
+    window: Optional[int] = None
+    kind: str = "biased_attention"
+
+
+@dataclass(frozen=True)
 class LatentAttentionSpec:
     """Causal attention whose keys and values are linear maps of a cached latent.  Per token the
     cache holds [c | k_rot]: c = rmsnorm(W_dkv h)[:kv_rank] * kv_norm and the rotated key part
@@ -141,12 +185,42 @@ class DenseFFSpec:
 
 @dataclass(frozen=True)
 class SwiGLUSpec:
+    """W_down (g sigmoid(slope g) (u + up_shift)) with g = W_gate h and u = W_up h; with a `limit`, g is
+    cut at limit from above and u clipped to [-limit, limit] first.  The defaults are SwiGLU."""
     hidden: int
     intermediate: int
     gate_proj: str                   # (intermediate, hidden)
     up_proj: str
     down_proj: str                   # (hidden, intermediate)
+    slope: float = 1.0
+    limit: Optional[float] = None
+    up_shift: float = 0.0
     kind: str = "swiglu"
+
+
+@dataclass(frozen=True)
+class RoutedFFSpec:
+    """A mixture of `n_experts` gated feed-forwards (each as SwiGLUSpec describes, `intermediate` wide) of
+    which a token uses `top`.  Scores s = sigmoid(W_router h) in float32; the experts with the largest
+    s + correction are chosen; their outputs are summed with weights s * route_scale (not renormalised).
+    Tensor names of expert e are the patterns with {e} filled in.  `shared`: a SwiGLUSpec that every token
+    runs through, added after multiplication by sigmoid(W_shared_gate h) where `shared_gate` is given."""
+    hidden: int
+    intermediate: int
+    n_experts: int
+    top: int
+    router: str                      # (n_experts, hidden)
+    gate_proj: str                   # pattern, (intermediate, hidden)
+    up_proj: str
+    down_proj: str                   # pattern, (hidden, intermediate)
+    correction: Optional[str] = None  # (n_experts,)
+    route_scale: float = 1.0
+    slope: float = 1.0
+    limit: Optional[float] = None
+    up_shift: float = 0.0
+    shared: Any = None
+    shared_gate: Optional[str] = None  # (1, hidden)
+    kind: str = "routed_ff"
 
 
 @dataclass(frozen=True)
@@ -179,7 +253,9 @@ class LayerSpec:
     (crates/model/src/llama.rs:264-271).  arrangement "sandwich": each sublayer's result is normed
     and scaled before it joins the stream, x += scale1 * post_norm1(mixer(norm1(x))) and the same
     with norm2, feed_forward, post_norm2, scale2; `feed_forward` None leaves the second sublayer out
-    (norm2, post_norm2 and scale2 are then None too)."""
+    (norm2, post_norm2 and scale2 are then None too).  arrangement "outnorm": the sublayers read the
+    stream itself and only their results are normed, x += residual_mult * norm1(mixer(x)), then x +=
+    residual_mult * norm2(feed_forward(x)), the second line only with a feed-forward."""
     norm1: Any
     mixer: Any
     norm2: Any
@@ -189,6 +265,7 @@ class LayerSpec:
     post_norm2: Any = None
     scale1: Optional[str] = None     # tensor name, shape (hidden,): per-channel scale of the sublayer's result
     scale2: Optional[str] = None
+    residual_mult: float = 1.0
 
 
 @dataclass(frozen=True)

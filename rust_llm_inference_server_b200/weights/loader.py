@@ -28,7 +28,8 @@ def check_checkpoint(expected: dict, ckpt: Checkpoint, ignorable=()) -> None:
     wrong = []
     for n in sorted(want & have):
         es, gs = tuple(expected[n]), tuple(ckpt.shape(n))
-        if es != gs:
+        # None in an expected shape: the checkpoint decides that extent
+        if len(es) != len(gs) or any(e is not None and e != g for e, g in zip(es, gs)):
             wrong.append(f"{n}: expected shape {list(es)}, checkpoint has {list(gs)}")
     if not (missing or unexpected or wrong):
         return
