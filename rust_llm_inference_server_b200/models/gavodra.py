@@ -31,7 +31,7 @@ def describe_gavodra(cfg: GavodraConfig) -> ModelSpec:
     W = cfg.width
     norm = lambda name: RMSNormSpec(W, cfg.eps, name)
     first_mix = next((i for i, l in enumerate(cfg.layers) if l.mixer.v_mix), None)
-    layers, order = [], []
+    layers, order, unread = [], [], []
     for i, layer in enumerate(cfg.layers):
         p, m = f"l{i}.", layer.mixer
         q = p + "mix."
@@ -40,8 +40,9 @@ def describe_gavodra(cfg: GavodraConfig) -> ModelSpec:
             hidden=W, n_heads=m.heads, n_kv_heads=m.kv_heads, dim=m.dim, v_dim=m.vdim, scale=m.scale, eps=cfg.eps,
             q_proj=q + "q", k_proj=q + "k", v_proj=q + "v", o_proj=q + "o", q_norm=q + "q.norm", k_norm=q + "k.norm",
             bias=DistanceBiasSpec(q + "rel", m.bias_rows, m.bias_max), head_gate=q + "g",
-            value_mix=q + "vmix" if mixes else None, value_source=m.v_mix and i == first_mix,
-            unused=() if mixes else (q + "vmix",))
+            value_mix=q + "vmix" if mixes else None, value_source=m.v_mix and i == first_mix)
+        if not mixes:
+            unread.append(q + "vmix")     # a mixing weight that a checkpoint may hold for a layer that mixes nothing
         ff = None
         if layer.mlp is not None and layer.mlp.kind == "dense":
             ff = _glu(W, p + "mlp.", layer.mlp.ff, layer.mlp.limit)
@@ -61,7 +62,7 @@ def describe_gavodra(cfg: GavodraConfig) -> ModelSpec:
         vocab_size=cfg.vocab, hidden=W, embedding=EmbeddingSpec(cfg.vocab, W, "embed", scale=cfg.embedding_scale),
         layers=tuple(layers), order=tuple(order), final_norm=norm("final.norm"),
         lm_head=LMHeadSpec(cfg.vocab, W, "embed", logit_scale=cfg.logit_scale, soft_cap=cfg.logit_softcap),
-        max_positions=cfg.max_positions, eos_token_ids=tuple(cfg.eos_token_ids))
+        max_positions=cfg.max_positions, ignorable=tuple(unread), eos_token_ids=tuple(cfg.eos_token_ids))
 
 
 def gavodra_tensor_kinds(cfg: GavodraConfig) -> dict:

@@ -869,7 +869,7 @@ def _set_stream_rows(value):
     STREAM_GEMM_ROWS = max(DECODE_GEMM_ROWS, min(int(value), STREAM_MAX_ROWS))
 
 
-library.PYTHON_SWITCHES.update(fuse_norms=_set_flag("FUSE_NORMS"), prefill_tcgen05=_set_flag("PREFILL_TCGEN05"),
+library.PYTHON_SWITCHES.update(biased_mma=_set_flag("BIASED_MMA"), moe_mma=_set_flag("MOE_MMA"), fuse_norms=_set_flag("FUSE_NORMS"), prefill_tcgen05=_set_flag("PREFILL_TCGEN05"),
                                latent_mma=_set_flag("LATENT_MMA"), latent_ctas_per_sm=_set_latent_ctas,
                                stream_rows=_set_stream_rows)
 
@@ -1000,13 +1000,30 @@ def qk_norm_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w, k
     return q_out
 
 
+BIASED_MMA = True          # debug switch "biased_mma": 0 takes the one-warp-a-row kernel for every size
+
+
+@functools.lru_cache(maxsize=None)
+def _biased_mma_sizes(dim: int, v_dim: int) -> bool:
+    return bool(lib().rlis_attention_bias_mma_takes(dim, v_dim))
+
+
 def biased_attention_takes_mma(dtype, n_heads: int, n_kv_heads: int, dim: int, v_dim: int) -> bool:
     """Whether the tensor-core kernels for attention with a bias by distance exist for these sizes."""
-    return False
+    return bool(BIASED_MMA and dtype == torch.bfloat16 and n_heads % n_kv_heads == 0
+                and _biased_mma_sizes(int(dim), int(v_dim)))
+
+
+@functools.lru_cache(maxsize=4096)
+def _biased_decode_pieces(n_decode: int, n_kv_heads: int, max_ctx: int, sms: int) -> int:
+    """Pieces a context is cut into for single tokens: a CTA takes one key/value head of one request, so
+    the context is cut until the CTAs fill the SMs about twice, in pieces of at least 256 keys."""
+    ctas = max(1, n_decode * n_kv_heads)
+    return max(1, min(2 * sms // ctas, max_ctx // 256, 64))
 
 
 def biased_decode_pieces(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
-    return 1
+    return _biased_decode_pieces(int(n_decode), int(n_kv_heads), max(1, int(max_ctx)), num_sms())
 
 
 def attention_biased(q, k_cache, v_cache, out, bias, gate, step, group: int, n_heads: int, n_kv_heads: int,
@@ -1015,27 +1032,62 @@ def attention_biased(q, k_cache, v_cache, out, bias, gate, step, group: int, n_h
     score = scale * q . k + bias[min(distance, len(bias) - 1), head]; a head's result is multiplied by
     sigmoid(gate[t, head]).  q [T, nh dim]; k_cache [pages, nkv, page_size, dim]; v_cache [pages, nkv,
     page_size, v_dim]; out [T, nh v_dim]; bias float32 [n_dist, nh] or None; gate [T, nh] (a column slice
-    of wider rows) or None."""
+    of wider rows) or None.
+
+    bfloat16 with sizes the tensor-core kernels take: single decoded tokens go to the split decode kernel
+    (groups of up to 16 query heads), portions of prompts (the step's tile list) to the flash kernel.
+    Everything else, and all of float32, to the kernel that takes one warp a (token, head)."""
     T = q.shape[0]
     _req(q, "q", None, (T, n_heads * dim))
     _req(out, "out", q.dtype, (T, n_heads * v_dim))
     _req(k_cache, "k_cache", q.dtype, (None, n_kv_heads, page_size, dim))
     _req(v_cache, "v_cache", q.dtype, (None, n_kv_heads, page_size, v_dim))
-    n_dist = 0
+    n_dist, bp = 0, None
     if bias is not None:
         _req(bias, "bias", torch.float32, (None, n_heads))
-        n_dist = bias.shape[0]
+        n_dist, bp = bias.shape[0], bias.data_ptr()
     gp, gs = None, 0
     if gate is not None:
         if gate.dtype != q.dtype or tuple(gate.shape) != (T, n_heads) or gate.stride(1) != 1 or not gate.is_cuda:
             raise KernelError("attention_biased: the gate must be [T, nh] rows with unit stride in q's type")
         gp, gs = gate.data_ptr(), gate.stride(0)
     tables = step.block_tables[group]
-    check(lib().rlis_attention_bias(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
-                                    bias.data_ptr() if bias is not None else None, n_dist, gp, gs,
-                                    step.seq_of_token.data_ptr(), step.positions.data_ptr(), tables.data_ptr(), None,
-                                    tables.shape[1], T, n_heads, n_kv_heads, dim, v_dim, page_size, float(scale),
-                                    int(window), _code(q.dtype), _stream()), "attention_bias")
+    fast = biased_attention_takes_mma(q.dtype, n_heads, n_kv_heads, dim, v_dim)
+    n_dec = getattr(step, "n_decode", 0) if fast and n_heads // n_kv_heads <= 16 else 0
+    n_tiles = getattr(step, "n_prefill_tiles", 0) if fast else 0
+    if n_dec:
+        pieces = biased_decode_pieces(n_dec, n_kv_heads, step.max_decode_ctx)
+        scratch = step.buffer("attn_partial", (n_dec * n_heads * pieces * (v_dim + 2),), torch.float32) if pieces > 1 else None
+        check(lib().rlis_attention_bias_decode(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+            scratch.data_ptr() if scratch is not None else None, bp, n_dist, gp, gs, step.dec_rows.data_ptr(),
+            step.dec_seqs.data_ptr(), step.ctx_lens.data_ptr(), tables.data_ptr(), tables.shape[1], n_dec, n_heads,
+            n_kv_heads, dim, v_dim, page_size, float(scale), int(window), pieces, _stream()), "attention_bias_decode")
+        _count("attention_bias.decode.mma" + (".split" if pieces > 1 else ""))
+    if n_tiles:
+        check(lib().rlis_attention_bias_prefill(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), bp, n_dist, gp, gs,
+            step.prefill_tiles.data_ptr(), n_tiles, step.cu_seqlens.data_ptr(), step.ctx_lens.data_ptr(),
+            tables.data_ptr(), tables.shape[1], n_heads, n_kv_heads, dim, v_dim, page_size, float(scale), int(window),
+            _stream()), "attention_bias_prefill")
+        _count("attention_bias.prefill.mma")
+    # what the tensor-core kernels did not take: nothing, the portions only, the single tokens only, or everything
+    rows, n_rows = None, T
+    if n_dec and n_tiles:
+        return out
+    if n_dec:
+        if step.n_prefill_tokens == 0:
+            return out
+        rows, n_rows = step.prefill_rows, step.n_prefill_tokens
+    elif n_tiles:
+        if getattr(step, "n_decode", 0) == 0:
+            return out
+        rows, n_rows = step.dec_rows, step.n_decode
+    check(lib().rlis_attention_bias(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), bp, n_dist, gp,
+                                    gs, step.seq_of_token.data_ptr(), step.positions.data_ptr(), tables.data_ptr(),
+                                    rows.data_ptr() if rows is not None else None, tables.shape[1], n_rows, n_heads,
+                                    n_kv_heads, dim, v_dim, page_size, float(scale), int(window), _code(q.dtype),
+                                    _stream()), "attention_bias")
     _count("attention_bias")
     return out
 
@@ -1048,9 +1100,28 @@ class MoePlan:
         self.__dict__.update(kw)
 
 
+MOE_MMA = True             # debug switch "moe_mma": 0 takes the FFMA products for bfloat16 too
+
+
 @functools.lru_cache(maxsize=None)
 def moe_tile_rows() -> int:
-    return int(lib().rlis_moe_tile_rows())
+    rows = int(lib().rlis_moe_tile_rows())
+    if int(lib().rlis_moe_mma_tile_rows()) != rows:
+        raise KernelError("the routed products disagree about the rows of a tile")
+    return rows
+
+
+def _moe_gemm(a, wg, wu, out, plan, N: int, K: int, glu: bool, slope: float, limit: float, shift: float, name: str):
+    """One of the routed products: tensor cores for bfloat16 rows that are 16-byte multiples, FFMA otherwise."""
+    args = (a.data_ptr(), wg.data_ptr(), wu.data_ptr() if wu is not None else None, out.data_ptr(),
+            plan.sorted_pair.data_ptr(), plan.tile_expert.data_ptr(), plan.max_tiles, plan.top, N, K, 1 if glu else 0,
+            float(slope), float(limit), float(shift))
+    if MOE_MMA and a.dtype == torch.bfloat16 and K % 8 == 0:
+        check(lib().rlis_moe_gemm_mma(*args, _stream()), name)
+        _count("moe_gemm.mma" + (".glu" if glu else ".down"))
+    else:
+        check(lib().rlis_moe_gemm(*args, _code(a.dtype), _stream()), name)
+        _count("moe_gemm" + (".glu" if glu else ".down"))
 
 
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: int, top: int, route_scale: float,
@@ -1095,10 +1166,7 @@ def moe_up(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, plan: MoeP
     _req(w_gate, "w_gate", x.dtype, (plan.n_experts, I, W))
     _req(w_up, "w_up", x.dtype, (plan.n_experts, I, W))
     act = step.buffer("moe_act", (plan.max_tiles * plan.tile, I), x.dtype)
-    check(lib().rlis_moe_gemm(x.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), act.data_ptr(),
-                              plan.sorted_pair.data_ptr(), plan.tile_expert.data_ptr(), plan.max_tiles, plan.top, I, W,
-                              1, float(slope), float(limit), float(up_shift), _code(x.dtype), _stream()), "moe_up")
-    _count("moe_gemm.glu")
+    _moe_gemm(x, w_gate, w_up, act, plan, I, W, True, slope, limit, up_shift, "moe_up")
     return act
 
 
@@ -1109,10 +1177,7 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan, step) -> to
     _req(act, "act", None, (plan.max_tiles * plan.tile, I))
     _req(w_down, "w_down", act.dtype, (plan.n_experts, W, I))
     y = step.buffer("moe_y", (S, W), torch.float32)
-    check(lib().rlis_moe_gemm(act.data_ptr(), w_down.data_ptr(), None, y.data_ptr(), plan.sorted_pair.data_ptr(),
-                              plan.tile_expert.data_ptr(), plan.max_tiles, plan.top, W, I, 0, 1.0, 0.0, 0.0,
-                              _code(act.dtype), _stream()), "moe_down")
-    _count("moe_gemm.down")
+    _moe_gemm(act, w_down, None, y, plan, W, I, False, 1.0, 0.0, 0.0, "moe_down")
     return y
 
 

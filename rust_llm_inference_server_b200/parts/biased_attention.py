@@ -82,8 +82,6 @@ class BiasedAttention(Mixer):
             out[s.head_gate] = (s.n_heads, s.hidden)
         if s.value_mix is not None:
             out[s.value_mix] = ()
-        for name in s.unused:
-            out[name] = ()
         return out
 
     def load(self, src) -> None:

@@ -112,8 +112,6 @@ class BiasedAttentionSpec:
     head_gate: Optional[str] = None  # (n_heads, hidden)
     value_mix: Optional[str] = None  # scalar tensor
     value_source: bool = False
-    # a tensor of the checkpoint that this layer does not read (a mixing weight on the source layer)
-    unused: tuple = ()
     window: Optional[int] = None
     kind: str = "biased_attention"
 

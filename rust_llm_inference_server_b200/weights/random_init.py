@@ -31,10 +31,10 @@ def _tensor_key(seed: int, name: str) -> list[int]:
 
 def random_tensor(seed: int, name: str, shape, kind: str, std: float = 0.02) -> torch.Tensor:
     rng = np.random.Generator(np.random.Philox(key=_tensor_key(seed, name)))
-    x = rng.standard_normal(size=tuple(shape), dtype=np.float32) * np.float32(_STD.get(kind, std))
+    x = np.asarray(rng.standard_normal(size=tuple(shape), dtype=np.float32) * np.float32(_STD.get(kind, std)))
     if kind == "norm":
-        x += np.float32(1.0)
-    return torch.from_numpy(x)
+        x = x + np.float32(1.0)
+    return torch.from_numpy(np.array(x, dtype=np.float32).reshape(tuple(shape)))
 
 
 def random_tensors(config_json: dict, seed: int, store_dtype: str = "bfloat16") -> dict:

@@ -55,7 +55,7 @@ def route(h, w_router, correction, top: int, scale: float):
 def routed_ff(h, W, p, mlp):
     """Mixture of experts with a gated shared expert."""
     r = mlp["router"]
-    idx, wts = route(h, W[p + "router"], W[p + "correction"], int(r["top"]), float(r["scale"]))
+    idx, wts = route(h, W[p + "router"], W[p + "correction"], int(r["top"]), float(r.get("scale", 1.0)))
     limit = float(mlp["expert"]["limit"])
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
@@ -107,8 +107,8 @@ def attention(h, W, p, m, eps, v_first, is_first):
 def forward(W, cfg, tokens, return_layers=False):
     """Logits [n, vocab] of one request's tokens (and the residual stream after every layer)."""
     eps = float(cfg["norm"]["eps"])
-    m_res = float(cfg["residual_mult"])
-    x = W["embed"][np.asarray(tokens)] * float(cfg["embedding"]["scale"])
+    m_res = float(cfg.get("residual_mult", 1.0))
+    x = W["embed"][np.asarray(tokens)] * float(cfg.get("embedding", {}).get("scale", 1.0))
     v_first, seen_mix, layers = None, False, []
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
@@ -122,7 +122,8 @@ def forward(W, cfg, tokens, return_layers=False):
             x = x + m_res * rms_norm(f, W[p + "norm2"], eps)
         layers.append(x.copy())
     y = rms_norm(x, W["final.norm"], eps)
-    logits = (y @ W["embed"].T) * float(cfg["logit_scale"])
-    cap = float(cfg["logit_softcap"])
-    logits = cap * np.tanh(logits / cap)
+    logits = (y @ W["embed"].T) * float(cfg.get("logit_scale", 1.0))
+    cap = cfg.get("logit_softcap")
+    if cap is not None:
+        logits = float(cap) * np.tanh(logits / float(cap))
     return (logits, np.stack(layers)) if return_layers else logits
