@@ -622,6 +622,126 @@ def workload_lasapel(args, torch, np) -> dict:
     return out
 
 
+def gavodra_config(width: int, vocab: int = 32000) -> dict:
+    """Four Gavodra layers at a real model's proportions: heads of 64 with four query heads a key head (as
+    the Llama layers beside them), a bias table of 32 rows reaching 128 positions back, one dense gated
+    feed-forward of 8/3 widths and three routed ones (32 experts of half a width, 4 a token, beside a shared
+    one of half a width: 2.5 widths of feed-forward a token)."""
+    H = width // 64
+    mix = {"heads": H, "kv_heads": max(1, H // 4), "dim": 64, "vdim": 64, "scale": 0.125, "bias_max": 128, "v_mix": True,
+           "bias_rows": 32}
+    moe = {"kind": "moe", "expert": {"ff": width // 2, "limit": 7.0}, "router": {"experts": 32, "top": 4, "scale": 2.5},
+           "shared": {"ff": width // 2, "limit": 7.0}}
+    dense = {"kind": "dense", "ff": width * 8 // 3 // 128 * 128, "limit": 7.0}
+    return {"architecture": "Gavodra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "embedding": {"scale": 8.0}, "logit_scale": 0.5, "logit_softcap": 30.0,
+            "layers": [{"type": "attention", "mixer": mix, "mlp": m} for m in (dense, moe, moe, moe)]}
+
+
+def gavodra_kernel_rooflines(width: int, B: int, ctx: int, T: int, pk: dict, torch, np) -> dict:
+    """The new kernels alone at the sizes of `gavodra_config(width)`, each beside the like kernel of the Llama
+    layers: {name: {"us", "ideal_us", "frac"}}.  Ideal: bytes that must move over the measured copy bandwidth
+    (single tokens) or FLOPs over the measured bfloat16 GEMM rate (prompts)."""
+    from rust_llm_inference_server_b200 import ops
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    page, nh, nkv, hd = 16, width // 64, max(1, width // 256), 64
+    E, top, ff = 32, 4, width // 2
+    bf, out = torch.bfloat16, {}
+    rnd = lambda *shape: torch.randn(*shape, device="cuda") * 0.3
+
+    def row(name, us, ideal_s):
+        out[name] = {"us": round(us, 1), "ideal_us": round(ideal_s * 1e6, 1), "frac": round(ideal_s * 1e6 / us, 3)}
+
+    bias = rnd(129, nh).contiguous()
+    for kind, reqs in (("decode", [(ctx - 1, 1)] * B), ("prefill", [(0, T)])):
+        st = _KernelStep(reqs, page, torch, np)
+        st.n_prefill_tokens = st.n_prefill_tokens if kind == "prefill" else 0
+        n, keys = st.n_tokens, (B * ctx if kind == "decode" else T * (T + 1) // 2)
+        kc, vc, q = rnd(st.n_pages, nkv, page, hd).to(bf), rnd(st.n_pages, nkv, page, hd).to(bf), rnd(n, nh * hd).to(bf)
+        gate = rnd(n, nh + 8).to(bf)[:, :nh]
+        o = torch.empty_like(q)
+        ideal = B * ctx * nkv * hd * 2 * 2 / hbm if kind == "decode" else 2 * nh * keys * 2 * hd / tf
+        us = _graph_time_us(lambda: ops.attention_biased(q, kc, vc, o, bias, gate, st, 0, nh, nkv, hd, hd, page, 0.125, 0), torch)
+        row(f"biased_attention_{kind}", us, ideal)
+        us = _graph_time_us(lambda: ops.attention(q, kc, vc, o, st, 0, nh, nkv, hd, page, 0.125, 0), torch)
+        row(f"gqa_attention_{kind}", us, ideal)
+        # the routed products (route + sort + both products + the weighted sum) beside Llama's gated
+        # feed-forward products at the same number of feed-forward columns a token (top * ff)
+        x = rnd(n, width).to(bf)
+        wr, corr = rnd(E, width).contiguous(), rnd(E).contiguous()
+        wg, wu, wd = rnd(E, ff, width).to(bf), rnd(E, ff, width).to(bf), rnd(E, width, ff).to(bf)
+        y = torch.empty(n, width, dtype=bf, device="cuda")
+
+        def routed():
+            plan = ops.moe_route(x, wr, corr, E, top, 2.5, False, st)
+            act = ops.moe_up(x, wg, wu, plan, 1.702, 7.0, 1.0, st)
+            return ops.moe_combine(ops.moe_down(act, wd, plan, st), plan, None, y)
+        used = min(E, n * top)
+        flops = 2.0 * n * top * 3 * ff * width
+        ideal = used * 3 * ff * width * 2 / hbm if kind == "decode" else flops / tf
+        row(f"routed_ff_{kind}", _graph_time_us(routed, torch), ideal)
+        I = top * ff
+        wgu = torch.stack([rnd(I // 4, 4, width), rnd(I // 4, 4, width)], dim=1).reshape(2 * I, width).to(bf).contiguous()
+        wdn = rnd(width, I).to(bf)
+
+        def gated():
+            if n <= ops.STREAM_GEMM_ROWS:
+                return ops.linear(ops.stream_gemm(x, wgu, swiglu4=True), wdn)
+            return ops.linear(ops.gemm_tcgen05(x, wgu, "swiglu4"), wdn)
+        row(f"gated_ff_{kind}", _graph_time_us(gated, torch), 3 * I * width * 2 / hbm if kind == "decode" else flops / tf)
+    return out
+
+
+def workload_gavodra(args, torch, np) -> dict:
+    """Prefill (one 2,048-token prompt) and decode (batch 8, context 4,096) of four Gavodra layers at two
+    widths beside four Llama layers of the same width, random bfloat16 weights; then the stages of one step
+    by CUDA-event spans (eager launches), and the new kernels alone, replayed from CUDA graphs, against
+    their rooflines beside Llama's like kernels."""
+    from rust_llm_inference_server_b200 import LLM
+    from rust_llm_inference_server_b200.ops import profile
+    pk, pk_src = peaks()
+    B, ctx, page, T = args.batch, args.context, 16, PREFILL_TOKENS
+    steps = min(args.steps, 64)
+    out = {"workload": "gavodra", "metric": "prefill and decode tokens/s of four layers, Gavodra beside Llama at equal width",
+           "unit": "tokens/s", "impl": "ours", "dtype": "bf16", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+           "data": "synthetic: uniform-random token ids, random-init weights (device generator)",
+           "config": {"global_batch": B, "seq_len": ctx, "prefill_tokens": T, "page_size": page, "layers": 4},
+           "peaks": dict(pk, source=pk_src), "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for width in (1024, 2048):
+        row = {}
+        for name, cfg in (("gavodra", gavodra_config(width)), ("llama", llama_config_like(width))):
+            llm = LLM.from_random(cfg, 8, dtype="bfloat16", on_device=True, max_seq_len=ctx + page,
+                                  num_blocks=B * (ctx + page) // page + 64, block_size=page, max_num_seqs=B,
+                                  max_batched_tokens=max(2048, B), prefix_caching=False)
+            pre = prefill_run(llm, T, 5, 3, torch, np)
+            ms, launches = decode_run(llm, B, steps, args.warmup, ctx, torch)
+            profile.enable(True)
+            prefill_run(llm, T, 3, 2, torch, np)
+            profile.take_report()
+            prefill_run(llm, T, 3, 0, torch, np)
+            pre_stages = {k: round(v[0] / 3 * 1e3, 1) for k, v in profile.take_report().items()}
+            decode_run(llm, B, 8, 4, ctx, torch, fill=False)
+            dec_stages = {k: round(v[0] / 8 * 1e3, 1) for k, v in profile.take_report().items()}
+            profile.enable(False)
+            row[name] = {"prefill_tokens_per_s": round(T / (pre / 1e3), 1), "prefill_ms": round(pre, 3),
+                         "decode_tokens_per_s": round(B / (ms / 1e3), 1), "decode_ms_per_step": round(ms, 4),
+                         "launches_per_decode_step": launches,
+                         "weight_bytes": int(sum(p.numel() * p.element_size() for p in _model_tensors(llm.model))),
+                         "prefill_stage_us": pre_stages, "decode_stage_us": dec_stages}
+            del llm
+            torch.cuda.empty_cache()
+        row["rooflines"] = gavodra_kernel_rooflines(width, B, ctx, T, pk, torch, np)
+        out["sizes"][f"width{width}"] = row
+    out["clocks"] = clocks.stop()
+    head = out["sizes"]["width2048"]["gavodra"]
+    out["value"] = head["decode_tokens_per_s"]
+    out["ms_per_step"] = head["decode_ms_per_step"]
+    out["gpu_launches"] = int(round(head["launches_per_decode_step"] * steps))
+    return out
+
+
 def _model_tensors(model):
     seen = {}
     for part in model.parts():
@@ -651,7 +771,8 @@ def print_timeline(records: list) -> None:
         prev = r["end"]
 
 
-WORKLOADS = {"3b": workload_3b, "8b": workload_8b, "1b-fp32": workload_1b_fp32, "lasapel": workload_lasapel}
+WORKLOADS = {"3b": workload_3b, "8b": workload_8b, "1b-fp32": workload_1b_fp32, "lasapel": workload_lasapel,
+             "gavodra": workload_gavodra}
 
 
 def main() -> int:

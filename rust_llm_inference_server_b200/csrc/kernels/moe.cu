@@ -4,8 +4,9 @@
 //            chosen (ties: the lower index); their weights are s * route_scale (no renormalisation).  An
 //            extra row of W_r, where given, is the logit of a gate on a shared expert: sigmoid of it.
 //   align:   the (token, choice) pairs are sorted by expert into slots; every expert's run of slots is
-//            padded to a multiple of the row tile, so a tile of rows belongs to one expert.  All on the
-//            device: no count ever reaches the host, and launches depend on the step's shape only.
+//            padded to a multiple of the row tile (32 rows, or 128 when there are many pairs an expert),
+//            so a tile of rows belongs to one expert.  All on the device: no count ever reaches the
+//            host, and launches depend on the step's shape only.
 //   up:      act[slot, :] = glu(W_gate_e x, W_up_e x) for the slot's token x and expert e
 //   down:    y[slot, :] = W_down_e act[slot, :]                         (float32)
 //   combine: out[t, :] = sum_k weight[t, k] * y[slot(t, k), :] + shared_gate[t] * shared[t, :]
@@ -18,76 +19,94 @@
 #include "common.cuh"
 #include <math.h>
 
-#define RLIS_MOE_TILE_M 32
-
 namespace {
-constexpr int BM = RLIS_MOE_TILE_M, BN = 64, BK = 16;
+constexpr int BM = 32, BN = 64, BK = 16;     // the FFMA product's own tile; a row tile of the sort is a multiple of BM
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-template <typename T>
+// A CTA takes TOK tokens: a warp forms one row of W_r against all of them, so the matrix is read once a
+// CTA (the tokens' rows come back from the first-level cache), then one warp a token chooses.
+template <typename T, int TOK>
 __global__ __launch_bounds__(128) void moe_route_kernel(
     const T* __restrict__ x, const float* __restrict__ w_router, const float* __restrict__ correction,
     int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ shared_gate,
-    int width, int n_experts, int top, float route_scale) {
+    int n_tokens, int width, int n_experts, int top, float route_scale) {
     pdl_wait_and_trigger();
     extern __shared__ float sm[];
-    float* z = sm;                          // [n_experts + 1]
-    float* choice = sm + n_experts + 1;     // [n_experts]
-    const int t = blockIdx.x;
+    const int stride = 2 * n_experts + 1;   // per token: z [n_experts + 1], choice [n_experts]
+    const int t0 = blockIdx.x * TOK;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    const T* row = x + (size_t)t * width;
     const int n_rows = n_experts + (shared_gate != nullptr ? 1 : 0);
     for (int e = warp; e < n_rows; e += nwarps) {
         const float* w = w_router + (size_t)e * width;
-        float dot = 0.f;
-        for (int k = lane; k < width; k += 32) dot = fmaf(w[k], to_f<T>(row[k]), dot);
-        dot = warp_sum(dot);
-        if (lane == 0) z[e] = dot;
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-        const float s = sigmoidf_(z[e]);
-        z[e] = s;
-        choice[e] = s + (correction != nullptr ? correction[e] : 0.f);
-    }
-    if (threadIdx.x == 0 && shared_gate != nullptr) shared_gate[t] = sigmoidf_(z[n_experts]);
-    __syncthreads();
-    if (warp != 0) return;
-    for (int k = 0; k < top; ++k) {
-        float best = -INFINITY;
-        int at = 0x7fffffff;
-        for (int e = lane; e < n_experts; e += 32) {
-            const float c = choice[e];
-            if (c > best || (c == best && e < at)) { best = c; at = e; }
+        float dot[TOK];
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) dot[i] = 0.f;
+        for (int k = lane; k < width; k += 32) {
+            const float wv = w[k];
+#pragma unroll
+            for (int i = 0; i < TOK; ++i) {
+                const int t = min(t0 + i, n_tokens - 1);
+                dot[i] = fmaf(wv, to_f<T>(x[(size_t)t * width + k]), dot[i]);
+            }
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        for (int i = 0; i < TOK; ++i) {
+            const float d = warp_sum(dot[i]);
+            if (lane == 0) sm[i * stride + e] = d;
         }
-        if (at >= n_experts) at = k;        // scores that compare with nothing (NaN): still a valid index
-        if (lane == 0) {
-            top_idx[(size_t)t * top + k] = at;
-            top_w[(size_t)t * top + k] = z[at] * route_scale;
-            choice[at] = -INFINITY;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < TOK * n_experts; idx += blockDim.x) {
+        const int i = idx / n_experts, e = idx - i * n_experts;
+        float* z = sm + i * stride;
+        const float s = sigmoidf_(z[e]);
+        z[e] = s;
+        z[n_experts + 1 + e] = s + (correction != nullptr ? correction[e] : 0.f);
+    }
+    if (threadIdx.x < TOK && shared_gate != nullptr && t0 + threadIdx.x < n_tokens)
+        shared_gate[t0 + threadIdx.x] = sigmoidf_(sm[threadIdx.x * stride + n_experts]);
+    __syncthreads();
+    for (int i = warp; i < TOK; i += nwarps) {
+        const int t = t0 + i;
+        if (t >= n_tokens) break;
+        float* z = sm + i * stride;
+        float* choice = z + n_experts + 1;
+        for (int k = 0; k < top; ++k) {
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int e = lane; e < n_experts; e += 32) {
+                const float c = choice[e];
+                if (c > best || (c == best && e < at)) { best = c; at = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            if (at >= n_experts) at = k;        // scores that compare with nothing (NaN): still a valid index
+            if (lane == 0) {
+                top_idx[(size_t)t * top + k] = at;
+                top_w[(size_t)t * top + k] = z[at] * route_scale;
+                choice[at] = -INFINITY;
+            }
+            __syncwarp();
         }
-        __syncwarp();
     }
 }
 
-// One CTA.  pairs = tokens * top.  sorted_pair [max_tiles * BM]: the pair in a slot or -1; pair_slot [pairs];
-// tile_expert [max_tiles]: the expert of a tile of BM slots or -1 (no such tile).
+// One CTA.  pairs = tokens * top.  sorted_pair [max_tiles * tile]: the pair in a slot or -1; pair_slot [pairs];
+// tile_expert [max_tiles]: the expert of a tile of `tile` slots or -1 (no such tile).
 __global__ __launch_bounds__(1024) void moe_align_kernel(
     const int* __restrict__ top_idx, int* __restrict__ sorted_pair, int* __restrict__ pair_slot,
-    int* __restrict__ tile_expert, int n_pairs, int n_experts, int max_tiles) {
+    int* __restrict__ tile_expert, int n_pairs, int n_experts, int max_tiles, int tile_rows) {
     pdl_wait_and_trigger();
     extern __shared__ int smi[];
     int* count = smi;                    // [n_experts]
     int* start = smi + n_experts;        // [n_experts]
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
-    for (int i = threadIdx.x; i < max_tiles * BM; i += blockDim.x) sorted_pair[i] = -1;
+    for (int i = threadIdx.x; i < max_tiles * tile_rows; i += blockDim.x) sorted_pair[i] = -1;
     __syncthreads();
     for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
         const int e = top_idx[i];
@@ -97,8 +116,8 @@ __global__ __launch_bounds__(1024) void moe_align_kernel(
     if (threadIdx.x == 0) {
         int tile = 0;
         for (int e = 0; e < n_experts; ++e) {
-            start[e] = tile * BM;
-            const int tiles = (count[e] + BM - 1) / BM;
+            start[e] = tile * tile_rows;
+            const int tiles = (count[e] + tile_rows - 1) / tile_rows;
             for (int i = 0; i < tiles && tile < max_tiles; ++i) tile_expert[tile++] = e;
             count[e] = 0;                // from here on: the next free slot of the expert's run
         }
@@ -109,7 +128,7 @@ __global__ __launch_bounds__(1024) void moe_align_kernel(
         const int e = top_idx[i];
         if (e < 0 || e >= n_experts) { pair_slot[i] = -1; continue; }
         const int slot = start[e] + atomicAdd(&count[e], 1);
-        if (slot >= max_tiles * BM) { pair_slot[i] = -1; continue; }    // the host sizes max_tiles so that this never happens
+        if (slot >= max_tiles * tile_rows) { pair_slot[i] = -1; continue; }    // the host sizes max_tiles so that this never happens
         sorted_pair[slot] = i;
         pair_slot[i] = slot;
     }
@@ -121,9 +140,9 @@ template <typename T, bool GLU>
 __global__ __launch_bounds__(256) void moe_gemm_kernel(
     const T* __restrict__ A, const T* __restrict__ Wg, const T* __restrict__ Wu, void* __restrict__ out_,
     const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert, int top, int N, int K,
-    float slope, float limit, float shift) {
+    float slope, float limit, float shift, int tile_rows) {
     pdl_wait();
-    const int e = tile_expert[blockIdx.y];
+    const int e = tile_expert[blockIdx.y * BM / tile_rows];
     if (e < 0) return;
     __shared__ float As[BK][BM + 4];
     __shared__ float Gs[BK][BN + 4];
@@ -230,7 +249,6 @@ __global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, in
 }
 }  // namespace
 
-extern "C" int rlis_moe_tile_rows() { return BM; }
 
 // x [T, width] in the element type; w_router float32 [n_experts (+ 1 with shared_gate), width];
 // correction float32 [n_experts] or null; top_idx int32 [T, top]; top_w float32 [T, top]; shared_gate
@@ -239,38 +257,43 @@ extern "C" int rlis_moe_route(const void* x, const float* w_router, const float*
                               float* top_w, float* shared_gate, int n_tokens, int width, int n_experts, int top,
                               float route_scale, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (n_experts <= 0 || top <= 0 || top > n_experts || n_experts > 4096) return RLIS_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(float);
-    if (dtype == RLIS_F32)
-        rlis_launch(moe_route_kernel<float>, n_tokens, 128, smem, stream, (const float*)x, w_router, correction, top_idx,
-                    top_w, shared_gate, width, n_experts, top, route_scale);
-    else if (dtype == RLIS_BF16)
-        rlis_launch(moe_route_kernel<bf16>, n_tokens, 128, smem, stream, (const bf16*)x, w_router, correction, top_idx,
-                    top_w, shared_gate, width, n_experts, top, route_scale);
-    else
-        return RLIS_ERR_UNSUPPORTED;
+    if (n_experts <= 0 || top <= 0 || top > n_experts || n_experts > 512) return RLIS_ERR_UNSUPPORTED;
+    // eight tokens a CTA when there are many (the router matrix is then read an eighth as often), one otherwise
+    const int tok = n_tokens >= 64 ? 8 : 1;
+    const size_t smem = (size_t)tok * (2 * n_experts + 1) * sizeof(float);
+    if (smem > 48 * 1024) return RLIS_ERR_UNSUPPORTED;
+    const unsigned blocks = (unsigned)((n_tokens + tok - 1) / tok);
+#define RLIS_ROUTE(T, TOK) rlis_launch(moe_route_kernel<T, TOK>, blocks, 128, smem, stream, (const T*)x, w_router, correction, \
+                                       top_idx, top_w, shared_gate, n_tokens, width, n_experts, top, route_scale)
+    if (dtype == RLIS_F32) { if (tok == 8) RLIS_ROUTE(float, 8); else RLIS_ROUTE(float, 1); }
+    else if (dtype == RLIS_BF16) { if (tok == 8) RLIS_ROUTE(bf16, 8); else RLIS_ROUTE(bf16, 1); }
+    else return RLIS_ERR_UNSUPPORTED;
+#undef RLIS_ROUTE
     return RLIS_LAUNCH_CHECK();
 }
 
 extern "C" int rlis_moe_align(const int* top_idx, int* sorted_pair, int* pair_slot, int* tile_expert, int n_pairs,
-                              int n_experts, int max_tiles, cudaStream_t stream) {
+                              int n_experts, int max_tiles, int tile_rows, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
-    if (n_experts <= 0 || n_experts > 4096 || max_tiles < (n_pairs + BM - 1) / BM) return RLIS_ERR_UNSUPPORTED;
+    if (n_experts <= 0 || n_experts > 4096 || tile_rows <= 0 || tile_rows % BM != 0 ||
+        max_tiles < (n_pairs + tile_rows - 1) / tile_rows)
+        return RLIS_ERR_UNSUPPORTED;
     rlis_launch(moe_align_kernel, 1, 1024, (size_t)2 * n_experts * sizeof(int), stream, top_idx, sorted_pair, pair_slot,
-                tile_expert, n_pairs, n_experts, max_tiles);
+                tile_expert, n_pairs, n_experts, max_tiles, tile_rows);
     return RLIS_LAUNCH_CHECK();
 }
 
-// glu != 0: A [T, K] rows of tokens, Wg and Wu [n_experts, N, K], out [max_tiles * tile, N] in the element type.
+// glu != 0: A [T, K] rows of tokens, Wg and Wu [n_experts, N, K], out [max_tiles * tile_rows, N] in the element type.
 // glu == 0: A [max_tiles * tile, K] rows of slots, Wg [n_experts, N, K], out float32 [max_tiles * tile, N].
 extern "C" int rlis_moe_gemm(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair,
-                             const int* tile_expert, int max_tiles, int top, int N, int K, int glu, float slope,
-                             float limit, float shift, int dtype, cudaStream_t stream) {
+                             const int* tile_expert, int max_tiles, int tile_rows, int top, int N, int K, int glu,
+                             float slope, float limit, float shift, int dtype, cudaStream_t stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
-    dim3 grid((N + BN - 1) / BN, max_tiles);
+    if (tile_rows <= 0 || tile_rows % BM != 0) return RLIS_ERR_UNSUPPORTED;
+    dim3 grid((N + BN - 1) / BN, max_tiles * (tile_rows / BM));
     if (grid.y > 65535) return RLIS_ERR_UNSUPPORTED;
 #define RLIS_MOE(T, G) rlis_launch(moe_gemm_kernel<T, G>, grid, 256, 0, stream, (const T*)A, (const T*)Wg, (const T*)Wu, \
-                                   out, sorted_pair, tile_expert, top, N, K, slope, limit, shift)
+                                   out, sorted_pair, tile_expert, top, N, K, slope, limit, shift, tile_rows)
     if (dtype == RLIS_F32) { if (glu) RLIS_MOE(float, true); else RLIS_MOE(float, false); }
     else if (dtype == RLIS_BF16) { if (glu) RLIS_MOE(bf16, true); else RLIS_MOE(bf16, false); }
     else return RLIS_ERR_UNSUPPORTED;

@@ -1,28 +1,33 @@
 // The routed feed-forward's two products on the tensor cores (bfloat16; moe.cu describes the layer and
-// holds the float32 products).  A tile of 32 slots belongs to one expert (the sort pads every expert's
-// run); a CTA of 4 warps forms 32 slots x 64 features of it with mma.sync m16n8k16 and float32 sums,
-// operands by 16-byte asynchronous copies in steps of 32 along k, double-buffered.  The first product
-// gathers its rows by token and forms gate and linear branch side by side, so the gating happens on the
-// accumulators and neither branch reaches memory; the second reads the slots' rows and leaves float32.
+// holds the float32 products).  A tile of TM slots (32, or 128 when there are many pairs an expert)
+// belongs to one expert (the sort pads every expert's run); a CTA forms TM slots x 64 features of it
+// with mma.sync m16n8k16 and float32 sums, a warp 16 slots x 32 features.  Operands arrive by 16-byte
+// asynchronous copies in steps of 64 along k through three stages, so two steps of weights are in
+// flight while one is multiplied: with a few tokens a step the products are a stream of expert weights
+// and live on bytes in flight.  The first product gathers its rows by token and forms gate and linear
+// branch side by side, so the gating happens on the accumulators and neither branch reaches memory;
+// the second reads the slots' rows and leaves float32.
 #include "common.cuh"
 #include "mma_utils.cuh"
 #include <math.h>
 
 namespace {
-constexpr int TM = 32, TN = 64, TK = 32, SA = TK + 8;
-constexpr int THREADS = 128;
+constexpr int TN = 64, TK = 64, SA = TK + 8, STAGES = 3;
 
-template <bool GLU>
-__global__ __launch_bounds__(THREADS) void moe_mma_kernel(
+template <bool GLU, int TM> struct MoeSmem { static constexpr int STAGE = (TM + TN * (GLU ? 2 : 1)) * SA; };
+
+template <bool GLU, int TM>
+__global__ __launch_bounds__(TM * 4) void moe_mma_kernel(
     const bf16* __restrict__ A, const bf16* __restrict__ Wg, const bf16* __restrict__ Wu, void* __restrict__ out_,
     const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert, int top, int N, int K,
     float slope, float limit, float shift) {
+    constexpr int THREADS = TM * 4;                  // TM / 16 x 2 warps
+    constexpr int STAGE = MoeSmem<GLU, TM>::STAGE;
     pdl_wait();
     const int e = tile_expert[blockIdx.y];
     if (e < 0) return;
-    __shared__ __align__(16) bf16 As[2][TM * SA];
-    __shared__ __align__(16) bf16 Gs[2][TN * SA];
-    __shared__ __align__(16) bf16 Us[GLU ? 2 : 1][GLU ? TN * SA : 8];
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sm = reinterpret_cast<bf16*>(smem_raw);     // [stage][A: TM x SA | G: TN x SA | U: TN x SA]
     __shared__ int rows[TM];
     const int slot0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
     if (threadIdx.x < TM) {
@@ -33,25 +38,32 @@ __global__ __launch_bounds__(THREADS) void moe_mma_kernel(
     const bf16* wg = Wg + (size_t)e * N * K;
     const bf16* wu = GLU ? Wu + (size_t)e * N * K : nullptr;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int wm = warp & 1, wn = warp >> 1;                  // 2 x 2 warps: 16 rows x 32 features each
+    const int wm = warp >> 1, wn = warp & 1;         // a warp: 16 slots x 32 features
     const int g = lane >> 2, c = lane & 3;
 
     auto issue = [&](int k0, int st) {
-        {   // 32 rows x 4 chunks of 8
-            const int r = threadIdx.x >> 2, ch = threadIdx.x & 3;
+        bf16* as = sm + (size_t)st * STAGE;
+        bf16* gs = as + TM * SA;
+        bf16* us = gs + TN * SA;
+#pragma unroll
+        for (int i = 0; i < (TM * 8) / THREADS; ++i) {      // TM rows x 8 chunks of 8
+            const int idx = threadIdx.x + i * THREADS;
+            const int r = idx >> 3, ch = idx & 7;
             const int gr = rows[r], gk = k0 + ch * 8;
             const bool ok = gr >= 0 && gk < K;
-            cp_async16(&As[st][r * SA + ch * 8], A + (ok ? (size_t)gr * K + gk : 0), ok);
+            cp_async16(as + r * SA + ch * 8, A + (ok ? (size_t)gr * K + gk : 0), ok);
         }
+        constexpr int WCH = TN * 8 * (GLU ? 2 : 1);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < (WCH + THREADS - 1) / THREADS; ++i) {
             const int idx = threadIdx.x + i * THREADS;
-            const int r = idx >> 2, ch = idx & 3;
+            if (WCH % THREADS != 0 && idx >= WCH) break;
+            const int which = idx / (TN * 8), rem = idx % (TN * 8);
+            const int r = rem >> 3, ch = rem & 7;
             const int gn = n0 + r, gk = k0 + ch * 8;
             const bool ok = gn < N && gk < K;
             const size_t off = ok ? (size_t)gn * K + gk : 0;
-            cp_async16(&Gs[st][r * SA + ch * 8], wg + off, ok);
-            if (GLU) cp_async16(&Us[st][r * SA + ch * 8], wu + off, ok);
+            cp_async16((which ? us : gs) + r * SA + ch * 8, (which ? wu : wg) + off, ok);
         }
         cp_async_commit();
     };
@@ -63,35 +75,39 @@ __global__ __launch_bounds__(THREADS) void moe_mma_kernel(
         for (int j = 0; j < 4; ++j) accg[i][j] = accu[i][j] = 0.f;
 
     const int nk = (K + TK - 1) / TK;
-    int st = 0;
-    issue(0, 0);
-    for (int kt = 0; kt < nk; ++kt) {
-        if (kt + 1 < nk) {
-            issue((kt + 1) * TK, st ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        uint32_t a[2][4];
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk)
-            ldmatrix_x4(a[kk], &As[st][(wm * 16 + (lane & 15)) * SA + kk * 16 + (lane >> 4) * 8]);
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            uint32_t b[4];
-            ldmatrix_x4(b, &Gs[st][(wn * 32 + nt * 8 + (lane & 7)) * SA + (lane >> 3) * 8]);
-            mma_bf16_16816(accg[nt], a[0], b[0], b[1]);
-            mma_bf16_16816(accg[nt], a[1], b[2], b[3]);
-            if (GLU) {
-                ldmatrix_x4(b, &Us[st][(wn * 32 + nt * 8 + (lane & 7)) * SA + (lane >> 3) * 8]);
-                mma_bf16_16816(accu[nt], a[0], b[0], b[1]);
-                mma_bf16_16816(accu[nt], a[1], b[2], b[3]);
-            }
-        }
-        __syncthreads();
-        st ^= 1;
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < nk) issue(s * TK, s);
+        else cp_async_commit();                      // an empty group keeps the count of groups in step
     }
+    for (int kt = 0; kt < nk; ++kt) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();                             // step kt has landed, and everyone is done with step kt - 1's stage
+        if (kt + STAGES - 1 < nk) issue((kt + STAGES - 1) * TK, (kt + STAGES - 1) % STAGES);
+        else cp_async_commit();
+        const bf16* as = sm + (size_t)(kt % STAGES) * STAGE;
+        const bf16* gs = as + TM * SA;
+        const bf16* us = gs + TN * SA;
+        uint32_t a[4][4];
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+            ldmatrix_x4(a[kk], as + (wm * 16 + (lane & 15)) * SA + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int k2 = 0; k2 < 2; ++k2) {
+                uint32_t b[4];
+                ldmatrix_x4(b, gs + (wn * 32 + nt * 8 + (lane & 7)) * SA + k2 * 32 + (lane >> 3) * 8);
+                mma_bf16_16816(accg[nt], a[2 * k2], b[0], b[1]);
+                mma_bf16_16816(accg[nt], a[2 * k2 + 1], b[2], b[3]);
+                if (GLU) {
+                    ldmatrix_x4(b, us + (wn * 32 + nt * 8 + (lane & 7)) * SA + k2 * 32 + (lane >> 3) * 8);
+                    mma_bf16_16816(accu[nt], a[2 * k2], b[0], b[1]);
+                    mma_bf16_16816(accu[nt], a[2 * k2 + 1], b[2], b[3]);
+                }
+            }
+    }
+    cp_async_wait<0>();
     pdl_trigger();
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -115,23 +131,34 @@ __global__ __launch_bounds__(THREADS) void moe_mma_kernel(
             }
     }
 }
-}  // namespace
 
-// The contract of rlis_moe_gemm (moe.cu) for bfloat16 operands whose k extent is a multiple of 8.
-extern "C" int rlis_moe_gemm_mma(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair,
-                                 const int* tile_expert, int max_tiles, int top, int N, int K, int glu, float slope,
-                                 float limit, float shift, cudaStream_t stream) {
-    if (max_tiles <= 0 || N <= 0) return 0;
-    if (K % 8 != 0 || K <= 0) return RLIS_ERR_UNSUPPORTED;
+template <bool GLU, int TM>
+int launch(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair, const int* tile_expert,
+           int max_tiles, int top, int N, int K, float slope, float limit, float shift, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)STAGES * MoeSmem<GLU, TM>::STAGE * sizeof(bf16);
+    static bool raised = false;
+    if (!raised) {
+        cudaFuncSetAttribute(moe_mma_kernel<GLU, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        raised = true;
+    }
     dim3 grid((N + TN - 1) / TN, max_tiles);
-    if (grid.y > 65535) return RLIS_ERR_UNSUPPORTED;
-    if (glu)
-        rlis_launch(moe_mma_kernel<true>, grid, THREADS, 0, stream, (const bf16*)A, (const bf16*)Wg, (const bf16*)Wu, out,
-                    sorted_pair, tile_expert, top, N, K, slope, limit, shift);
-    else
-        rlis_launch(moe_mma_kernel<false>, grid, THREADS, 0, stream, (const bf16*)A, (const bf16*)Wg, (const bf16*)Wu, out,
-                    sorted_pair, tile_expert, top, N, K, slope, limit, shift);
+    rlis_launch(moe_mma_kernel<GLU, TM>, grid, TM * 4, smem, stream, (const bf16*)A, (const bf16*)Wg, (const bf16*)Wu, out,
+                sorted_pair, tile_expert, top, N, K, slope, limit, shift);
     return RLIS_LAUNCH_CHECK();
 }
+}  // namespace
 
-extern "C" int rlis_moe_mma_tile_rows() { return TM; }
+// The contract of rlis_moe_gemm (moe.cu) for bfloat16 operands whose k extent is a multiple of 8 and row
+// tiles of 32 or 128 slots.
+extern "C" int rlis_moe_gemm_mma(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair,
+                                 const int* tile_expert, int max_tiles, int tile_rows, int top, int N, int K, int glu,
+                                 float slope, float limit, float shift, cudaStream_t stream) {
+    if (max_tiles <= 0 || N <= 0) return 0;
+    if (K % 8 != 0 || K <= 0 || max_tiles > 65535 || (tile_rows != 32 && tile_rows != 128)) return RLIS_ERR_UNSUPPORTED;
+#define RLIS_MM(G, T) launch<G, T>(A, Wg, Wu, out, sorted_pair, tile_expert, max_tiles, top, N, K, slope, limit, shift, stream)
+    if (tile_rows == 32) return glu ? RLIS_MM(true, 32) : RLIS_MM(false, 32);
+    return glu ? RLIS_MM(true, 128) : RLIS_MM(false, 128);
+#undef RLIS_MM
+}
+
+extern "C" int rlis_moe_mma_takes_tile(int tile_rows) { return tile_rows == 32 || tile_rows == 128; }

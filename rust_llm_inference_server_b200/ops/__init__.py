@@ -1103,20 +1103,18 @@ class MoePlan:
 MOE_MMA = True             # debug switch "moe_mma": 0 takes the FFMA products for bfloat16 too
 
 
-@functools.lru_cache(maxsize=None)
-def moe_tile_rows() -> int:
-    rows = int(lib().rlis_moe_tile_rows())
-    if int(lib().rlis_moe_mma_tile_rows()) != rows:
-        raise KernelError("the routed products disagree about the rows of a tile")
-    return rows
+def moe_tile_rows(n_pairs: int, n_experts: int) -> int:
+    """Rows of a tile of the sort: 128 when an expert gets about a tile's worth of pairs or more (a prompt's
+    portion: wide tiles read the weights fewer times), else 32 (a few tokens: little padding)."""
+    return 128 if n_pairs >= 96 * n_experts else 32
 
 
 def _moe_gemm(a, wg, wu, out, plan, N: int, K: int, glu: bool, slope: float, limit: float, shift: float, name: str):
     """One of the routed products: tensor cores for bfloat16 rows that are 16-byte multiples, FFMA otherwise."""
     args = (a.data_ptr(), wg.data_ptr(), wu.data_ptr() if wu is not None else None, out.data_ptr(),
-            plan.sorted_pair.data_ptr(), plan.tile_expert.data_ptr(), plan.max_tiles, plan.top, N, K, 1 if glu else 0,
-            float(slope), float(limit), float(shift))
-    if MOE_MMA and a.dtype == torch.bfloat16 and K % 8 == 0:
+            plan.sorted_pair.data_ptr(), plan.tile_expert.data_ptr(), plan.max_tiles, plan.tile, plan.top, N, K,
+            1 if glu else 0, float(slope), float(limit), float(shift))
+    if MOE_MMA and a.dtype == torch.bfloat16 and K % 8 == 0 and lib().rlis_moe_mma_takes_tile(plan.tile):
         check(lib().rlis_moe_gemm_mma(*args, _stream()), name)
         _count("moe_gemm.mma" + (".glu" if glu else ".down"))
     else:
@@ -1136,7 +1134,7 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: in
     if correction is not None:
         _req(correction, "correction", torch.float32, (n_experts,))
     pairs = T * top
-    tile = moe_tile_rows()
+    tile = moe_tile_rows(pairs, n_experts)
     max_tiles = min(pairs, n_experts) + pairs // tile      # every expert in use ends in at most one partial tile
     ints = step.buffer("moe_ints", (2 * pairs + max_tiles * tile + max_tiles,), torch.int32)
     flts = step.buffer("moe_floats", (pairs + T,), torch.float32)
@@ -1149,7 +1147,7 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: in
                                n_experts, top, float(route_scale), _code(x.dtype), _stream()), "moe_route")
     _count("moe_route")
     check(lib().rlis_moe_align(top_idx.data_ptr(), sorted_pair.data_ptr(), pair_slot.data_ptr(), tile_expert.data_ptr(),
-                               pairs, n_experts, max_tiles, _stream()), "moe_align")
+                               pairs, n_experts, max_tiles, tile, _stream()), "moe_align")
     _count("moe_align")
     return MoePlan(n_tokens=T, top=top, n_experts=n_experts, tile=tile, max_tiles=max_tiles, top_idx=top_idx,
                    top_w=top_w, pair_slot=pair_slot, sorted_pair=sorted_pair, tile_expert=tile_expert,

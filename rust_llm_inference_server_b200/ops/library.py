@@ -44,12 +44,11 @@ SIGNATURES = {
     "rlis_attention_bias_mma_takes": [I, I],
     "rlis_attention_bias_prefill": [P, P, P, P, P, I, P, LL, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
     "rlis_attention_bias_decode": [P, P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
-    "rlis_moe_tile_rows": [],
     "rlis_moe_route": [P, P, P, P, P, P, I, I, I, I, F, I, P],
-    "rlis_moe_align": [P, P, P, P, I, I, I, P],
-    "rlis_moe_gemm": [P, P, P, P, P, P, I, I, I, I, I, F, F, F, I, P],
-    "rlis_moe_gemm_mma": [P, P, P, P, P, P, I, I, I, I, I, F, F, F, P],
-    "rlis_moe_mma_tile_rows": [],
+    "rlis_moe_align": [P, P, P, P, I, I, I, I, P],
+    "rlis_moe_gemm": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, I, P],
+    "rlis_moe_gemm_mma": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, P],
+    "rlis_moe_mma_takes_tile": [I],
     "rlis_moe_combine": [P, P, P, P, P, P, I, I, I, I, P],
     "rlis_glu_act": [P, P, I, I, F, F, F, I, P],
     "rlis_rope_cache": [P, P, P, P, P, P, P, I, I, I, I, I, I, P],

@@ -286,7 +286,8 @@ def test_attention_far_keys_table_rows_page_borders_and_gates(dtype, H, G, d, dv
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,E,top,W,I", [(1, 3, 1, 40, 24), (37, 5, 2, 96, 40), (150, 8, 3, 64, 72), (64, 4, 4, 32, 16)])
+@pytest.mark.parametrize("T,E,top,W,I", [(1, 3, 1, 40, 24), (37, 5, 2, 96, 40), (150, 8, 3, 64, 72), (64, 4, 4, 32, 16),
+                                          (300, 3, 2, 64, 48)])         # the last: wide tiles of the sort
 def test_routing_choice_sort_and_experts(dtype, T, E, top, W, I):
     from rust_llm_inference_server_b200 import ops
     rng = np.random.default_rng(T)
@@ -304,6 +305,7 @@ def test_routing_choice_sort_and_experts(dtype, T, E, top, W, I):
     # the sort: every pair sits in exactly one slot, of a tile of its expert
     sp, ps, te = plan.sorted_pair.cpu().numpy(), plan.pair_slot.cpu().numpy(), plan.tile_expert.cpu().numpy()
     assert sorted(sp[sp >= 0].tolist()) == list(range(T * top))
+    assert plan.tile == (128 if T == 300 else 32)
     for pair in range(T * top):
         assert sp[ps[pair]] == pair and te[ps[pair] // plan.tile] == idx.reshape(-1)[pair]
     wg, wu = (dev(rng.standard_normal((E, I, W)) / np.sqrt(W), dtype) for _ in range(2))
