@@ -1,7 +1,7 @@
 // Tensor-core kernels (bfloat16) for the attention that attention_bias.cu describes: normed queries and
 // keys, score = scale * q . k + bias[min(distance, n_dist - 1), head], keys of width D and values of
 // width DV, a gate on every head's result.  mma.sync m16n8k16 with float32 sums; keys and values reach
-// shared memory by 16-byte asynchronous copies, double-buffered, in tiles of 64 keys; rows padded by 8
+// shared memory by 16-byte asynchronous copies, two or three stages deep, in tiles of 64 keys; rows padded by 8
 // elements so that ldmatrix is free of bank conflicts; softmax in float32 in units of log2(e).
 //
 // Portions of prompts: one CTA = one query head x 64 tokens of one request (4 warps x 16 rows); the
@@ -28,6 +28,11 @@ constexpr float LOG2E = 1.4426950408889634f;
 template <int D, int DV> struct Stage { static constexpr int ELEMS = BN * (D + 8) + BN * (DV + 8); };
 template <int D, int DV> constexpr size_t smem_bytes() {
     return (size_t)2 * Stage<D, DV>::ELEMS * sizeof(bf16) + 2 * 128 * sizeof(float);
+}
+// single tokens: three stages (two tiles of keys in flight while one is used: the kernel lives on bytes in flight)
+constexpr int DEC_STAGES = 3;
+template <int D, int DV> constexpr size_t decode_smem_bytes() {
+    return (size_t)DEC_STAGES * Stage<D, DV>::ELEMS * sizeof(bf16);
 }
 
 // Brings tile `kt` of a request's keys and values into stage memory (ks_, vs_); keys outside [k_lo, k_hi) are zeros.
@@ -64,8 +69,9 @@ __device__ __forceinline__ void issue_tile(bf16* ks_, bf16* vs_, const bf16* kba
     }
 }
 
+// (four CTAs an SM for the narrow heads, three for the wide ones: the bound keeps the registers under that)
 template <int D, int DV>
-__global__ __launch_bounds__(THREADS) void attn_bias_prefill_kernel(
+__global__ __launch_bounds__(THREADS, (D + DV <= 128) ? 4 : 3) void attn_bias_prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     bf16* __restrict__ out, const float* __restrict__ bias, int n_dist, const bf16* __restrict__ gate,
     long long gate_stride, const int* __restrict__ tiles, const int* __restrict__ cu_seqlens,
@@ -322,16 +328,17 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
 #pragma unroll
         for (int e = 0; e < 4; ++e) oacc[nd][e] = 0.f;
 
-    int stage = 0;
-    if (kt0 < kt1) issue(kt0, 0);
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; ++s) {
+        if (kt0 + s < kt1) issue(kt0 + s, s);
+        else cp_async_commit();                      // an empty group keeps the count of groups in step
+    }
     for (int kt = kt0; kt < kt1; ++kt) {
-        if (kt + 1 < kt1) {
-            issue(kt + 1, stage ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        const int stage = (kt - kt0) % DEC_STAGES;
+        cp_async_wait<DEC_STAGES - 2>();
+        __syncthreads();                             // tile kt has landed, and everyone is done with the stage of tile kt - 1
+        if (kt + DEC_STAGES - 1 < kt1) issue(kt + DEC_STAGES - 1, (kt - kt0 + DEC_STAGES - 1) % DEC_STAGES);
+        else cp_async_commit();
         const bf16* ks_ = sbase + (size_t)stage * Stage<D, DV>::ELEMS;
         const bf16* vs_ = ks_ + BN * SK;
         const int key0 = kt * BN + warp * 16;              // this warp's 16 keys of the tile
@@ -417,9 +424,9 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
                 mma_bf16_16816(oacc[2 * nd2 + 1], pa, vb[2], vb[3]);
             }
         }
-        __syncthreads();
-        stage ^= 1;
     }
+    cp_async_wait<0>();
+    __syncthreads();
     pdl_trigger();
     // the four warps' states meet in shared memory (the stages are free now): [warp][row][DV + 2]
     float* mg = reinterpret_cast<float*>(smem_raw);
@@ -500,7 +507,7 @@ bool sizes_taken(int d, int dv) { return (d == 64 || d == 128) && (dv == 32 || d
 
 template <int D, int DV> void raise_smem_limits() {
     cudaFuncSetAttribute(attn_bias_prefill_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<D, DV>());
-    cudaFuncSetAttribute(attn_bias_decode_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<D, DV>());
+    cudaFuncSetAttribute(attn_bias_decode_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes<D, DV>());
 }
 void raise_all_once() {
     static bool done = false;
@@ -551,7 +558,7 @@ extern "C" int rlis_attention_bias_decode(const void* q, const void* k_cache, co
         return RLIS_ERR_UNSUPPORTED;
     raise_all_once();
     dim3 grid(nkv, n_dec, pieces);
-#define RLIS_AB_DEC(D_, DV_) rlis_launch(attn_bias_decode_kernel<D_, DV_>, grid, THREADS, smem_bytes<D_, DV_>(), stream, \
+#define RLIS_AB_DEC(D_, DV_) rlis_launch(attn_bias_decode_kernel<D_, DV_>, grid, THREADS, decode_smem_bytes<D_, DV_>(), stream, \
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, partial, bias, n_dist,                 \
         (const bf16*)gate, gate_stride, dec_rows, dec_seqs, ctx_lens, block_tables, max_blocks, nh, nkv, page_size,   \
         scale, window, pieces)

@@ -24,10 +24,11 @@ constexpr int BM = 32, BN = 64, BK = 16;     // the FFMA product's own tile; a r
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-// A CTA takes TOK tokens: a warp forms one row of W_r against all of them, so the matrix is read once a
-// CTA (the tokens' rows come back from the first-level cache), then one warp a token chooses.
+// A CTA takes TOK tokens and has a warp for every row of W_r (up to 32 warps): a warp forms its row against
+// all of the CTA's tokens, so the matrix is read once a CTA (the tokens' rows come back from the first-level
+// cache) and the rows' sums run side by side; then one warp a token chooses.
 template <typename T, int TOK>
-__global__ __launch_bounds__(128) void moe_route_kernel(
+__global__ __launch_bounds__(1024) void moe_route_kernel(
     const T* __restrict__ x, const float* __restrict__ w_router, const float* __restrict__ correction,
     int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ shared_gate,
     int n_tokens, int width, int n_experts, int top, float route_scale) {
@@ -42,12 +43,30 @@ __global__ __launch_bounds__(128) void moe_route_kernel(
         float dot[TOK];
 #pragma unroll
         for (int i = 0; i < TOK; ++i) dot[i] = 0.f;
-        for (int k = lane; k < width; k += 32) {
-            const float wv = w[k];
+        if ((width & 3) == 0) {
+            // four elements a lane and step (16-byte loads of the matrix, four of a token's row)
+#pragma unroll 4
+            for (int k = lane * 4; k < width; k += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + k);
 #pragma unroll
-            for (int i = 0; i < TOK; ++i) {
-                const int t = min(t0 + i, n_tokens - 1);
-                dot[i] = fmaf(wv, to_f<T>(x[(size_t)t * width + k]), dot[i]);
+                for (int i = 0; i < TOK; ++i) {
+                    const int t = min(t0 + i, n_tokens - 1);
+                    const T* xr = x + (size_t)t * width + k;
+                    dot[i] = fmaf(wv.x, to_f<T>(xr[0]), dot[i]);
+                    dot[i] = fmaf(wv.y, to_f<T>(xr[1]), dot[i]);
+                    dot[i] = fmaf(wv.z, to_f<T>(xr[2]), dot[i]);
+                    dot[i] = fmaf(wv.w, to_f<T>(xr[3]), dot[i]);
+                }
+            }
+        } else {
+#pragma unroll 4
+            for (int k = lane; k < width; k += 32) {
+                const float wv = w[k];
+#pragma unroll
+                for (int i = 0; i < TOK; ++i) {
+                    const int t = min(t0 + i, n_tokens - 1);
+                    dot[i] = fmaf(wv, to_f<T>(x[(size_t)t * width + k]), dot[i]);
+                }
             }
         }
 #pragma unroll
@@ -263,7 +282,9 @@ extern "C" int rlis_moe_route(const void* x, const float* w_router, const float*
     const size_t smem = (size_t)tok * (2 * n_experts + 1) * sizeof(float);
     if (smem > 48 * 1024) return RLIS_ERR_UNSUPPORTED;
     const unsigned blocks = (unsigned)((n_tokens + tok - 1) / tok);
-#define RLIS_ROUTE(T, TOK) rlis_launch(moe_route_kernel<T, TOK>, blocks, 128, smem, stream, (const T*)x, w_router, correction, \
+    const int rows = n_experts + (shared_gate != nullptr ? 1 : 0);
+    const unsigned threads = 32u * (unsigned)(rows < 32 ? (rows < tok ? tok : rows) : 32);
+#define RLIS_ROUTE(T, TOK) rlis_launch(moe_route_kernel<T, TOK>, blocks, threads, smem, stream, (const T*)x, w_router, correction, \
                                        top_idx, top_w, shared_gate, n_tokens, width, n_experts, top, route_scale)
     if (dtype == RLIS_F32) { if (tok == 8) RLIS_ROUTE(float, 8); else RLIS_ROUTE(float, 1); }
     else if (dtype == RLIS_BF16) { if (tok == 8) RLIS_ROUTE(bf16, 8); else RLIS_ROUTE(bf16, 1); }

@@ -1017,9 +1017,9 @@ def biased_attention_takes_mma(dtype, n_heads: int, n_kv_heads: int, dim: int, v
 @functools.lru_cache(maxsize=4096)
 def _biased_decode_pieces(n_decode: int, n_kv_heads: int, max_ctx: int, sms: int) -> int:
     """Pieces a context is cut into for single tokens: a CTA takes one key/value head of one request, so
-    the context is cut until the CTAs fill the SMs about twice, in pieces of at least 256 keys."""
+    the context is cut until there are about four CTAs an SM, in pieces of at least 128 keys."""
     ctas = max(1, n_decode * n_kv_heads)
-    return max(1, min(2 * sms // ctas, max_ctx // 256, 64))
+    return max(1, min(-(-4 * sms // ctas), max_ctx // 128, 64))
 
 
 def biased_decode_pieces(n_decode: int, n_kv_heads: int, max_ctx: int) -> int:
