@@ -25,6 +25,13 @@ static_assert(BM == RLIS_PREFILL_TILE, "the host's tile list is cut for another 
 constexpr int BN = 64;   // keys per tile
 constexpr float LOG2E = 1.4426950408889634f;
 
+// 2^x in one instruction (relative error 2^-22; arguments here are at most 0, and -inf gives 0).
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int D, int DV> struct Stage { static constexpr int ELEMS = BN * (D + 8) + BN * (DV + 8); };
 template <int D, int DV> constexpr size_t smem_bytes() {
     return (size_t)2 * Stage<D, DV>::ELEMS * sizeof(bf16) + 2 * 128 * sizeof(float);
@@ -39,7 +46,8 @@ template <int D, int DV> constexpr size_t decode_smem_bytes() {
 template <int D, int DV>
 __device__ __forceinline__ void issue_tile(bf16* ks_, bf16* vs_, const bf16* kbase, const bf16* vbase,
                                            const int* table, int kt, int k_lo, int k_hi, int page_size,
-                                           size_t page_stride_k, size_t page_stride_v) {
+                                           int page_shift, size_t page_stride_k, size_t page_stride_v) {
+    // (page_shift: log2 of a power-of-two page size, or -1; a shift instead of a division a row)
     constexpr int CK = D / 8, CV = DV / 8;
 #pragma unroll
     for (int i = 0; i < (BN * CK) / THREADS; ++i) {
@@ -49,8 +57,8 @@ __device__ __forceinline__ void issue_tile(bf16* ks_, bf16* vs_, const bf16* kba
         const bool valid = key < k_hi && key >= k_lo;
         size_t off = 0;
         if (valid) {
-            const int pi = key / page_size;
-            off = (size_t)table[pi] * page_stride_k + (size_t)(key - pi * page_size) * D + c16 * 8;
+            const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+            off = (size_t)table[pi] * page_stride_k + (size_t)((key - pi * page_size) * D + c16 * 8);
         }
         cp_async16(ks_ + kin * (D + 8) + c16 * 8, kbase + off, valid);
     }
@@ -62,8 +70,8 @@ __device__ __forceinline__ void issue_tile(bf16* ks_, bf16* vs_, const bf16* kba
         const bool valid = key < k_hi && key >= k_lo;
         size_t off = 0;
         if (valid) {
-            const int pi = key / page_size;
-            off = (size_t)table[pi] * page_stride_v + (size_t)(key - pi * page_size) * DV + c16 * 8;
+            const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+            off = (size_t)table[pi] * page_stride_v + (size_t)((key - pi * page_size) * DV + c16 * 8);
         }
         cp_async16(vs_ + kin * (DV + 8) + c16 * 8, vbase + off, valid);
     }
@@ -119,13 +127,14 @@ __global__ __launch_bounds__(THREADS, (D + DV <= 128) ? 4 : 3) void attn_bias_pr
     const int k_lo = window > 0 ? max(0, start_pos + t0 - window + 1) : 0;
     const int kt0 = k_lo / BN, kt1 = (k_hi + BN - 1) / BN;
     const size_t psk = (size_t)nkv * page_size * D, psv = (size_t)nkv * page_size * DV;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
     const bf16* kbase = k_cache + (size_t)kvh * page_size * D;
     const bf16* vbase = v_cache + (size_t)kvh * page_size * DV;
     const float far_bias = bias != nullptr ? bias[(size_t)(n_dist - 1) * nh + head] * LOG2E : 0.f;
 
     auto issue = [&](int kt, int stage) {
         bf16* ks_ = sbase + (size_t)stage * Stage<D, DV>::ELEMS;
-        issue_tile<D, DV>(ks_, ks_ + BN * SK, kbase, vbase, table, kt, k_lo, k_hi, page_size, psk, psv);
+        issue_tile<D, DV>(ks_, ks_ + BN * SK, kbase, vbase, table, kt, k_lo, k_hi, page_size, page_shift, psk, psv);
         // the tile's distances: row r, key column j are dist0 + r + (BN - 1 - j) apart
         const int dist0 = start_pos + t0 - (kt * BN + BN - 1);
         if (bias != nullptr && dist0 < n_dist - 1 && threadIdx.x < 2 * BN - 1) {
@@ -173,36 +182,51 @@ __global__ __launch_bounds__(THREADS, (D + DV <= 128) ? 4 : 3) void attn_bias_pr
         const bool edge = (kt + 1) * BN - 1 > start_pos + t0 + warp * 16 || window > 0;
         const bool near = bias != nullptr && start_pos + t0 - (kt * BN + BN - 1) < n_dist - 1;
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        if (!edge && !near) {
+            // most tiles of a long prompt: every key is seen by every row, and all share the table's last row
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+            for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int j = nt * 8 + 2 * c + e;
-                float s0 = fmaf(sacc[nt][e], scale_log2, near ? bs[r0 + BN - 1 - j] : far_bias);
-                float s1 = fmaf(sacc[nt][2 + e], scale_log2, near ? bs[r1 + BN - 1 - j] : far_bias);
-                if (edge) {
-                    const int key = kt * BN + j;
-                    if (!(key <= pos0 && key >= lo0)) s0 = -INFINITY;
-                    if (!(key <= pos1 && key >= lo1)) s1 = -INFINITY;
+                for (int e = 0; e < 2; ++e) {
+                    const float s0 = fmaf(sacc[nt][e], scale_log2, far_bias);
+                    const float s1 = fmaf(sacc[nt][2 + e], scale_log2, far_bias);
+                    sacc[nt][e] = s0;
+                    sacc[nt][2 + e] = s1;
+                    mx0 = fmaxf(mx0, s0);
+                    mx1 = fmaxf(mx1, s1);
                 }
-                sacc[nt][e] = s0;
-                sacc[nt][2 + e] = s1;
-                mx0 = fmaxf(mx0, s0);
-                mx1 = fmaxf(mx1, s1);
-            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = nt * 8 + 2 * c + e;
+                    float s0 = fmaf(sacc[nt][e], scale_log2, near ? bs[r0 + BN - 1 - j] : far_bias);
+                    float s1 = fmaf(sacc[nt][2 + e], scale_log2, near ? bs[r1 + BN - 1 - j] : far_bias);
+                    if (edge) {
+                        const int key = kt * BN + j;
+                        if (!(key <= pos0 && key >= lo0)) s0 = -INFINITY;
+                        if (!(key <= pos1 && key >= lo1)) s1 = -INFINITY;
+                    }
+                    sacc[nt][e] = s0;
+                    sacc[nt][2 + e] = s1;
+                    mx0 = fmaxf(mx0, s0);
+                    mx1 = fmaxf(mx1, s1);
+                }
+        }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
         const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float corr0 = exp2f(m_run[0] - ms0), corr1 = exp2f(m_run[1] - ms1);
+        const float corr0 = ex2(m_run[0] - ms0), corr1 = ex2(m_run[1] - ms1);
         float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const float p0 = exp2f(sacc[nt][e] - ms0), p1 = exp2f(sacc[nt][2 + e] - ms1);
+                const float p0 = ex2(sacc[nt][e] - ms0), p1 = ex2(sacc[nt][2 + e] - ms1);
                 sacc[nt][e] = p0;
                 sacc[nt][2 + e] = p1;
                 ls0 += p0;
@@ -307,6 +331,7 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
     const int per = (t_all + pieces - 1) / pieces;
     const int kt0 = t_first + piece * per, kt1 = min(kt0 + per, t_first + t_all);
     const size_t psk = (size_t)nkv * page_size * D, psv = (size_t)nkv * page_size * DV;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
     const bf16* kbase = k_cache + (size_t)kvh * page_size * D;
     const bf16* vbase = v_cache + (size_t)kvh * page_size * DV;
     const float* brow0 = bias != nullptr ? bias + (rv0 ? h0 : 0) : nullptr;
@@ -316,7 +341,7 @@ __global__ __launch_bounds__(THREADS) void attn_bias_decode_kernel(
 
     auto issue = [&](int kt, int stage) {
         bf16* ks_ = sbase + (size_t)stage * Stage<D, DV>::ELEMS;
-        issue_tile<D, DV>(ks_, ks_ + BN * SK, kbase, vbase, table, kt, k_lo, k_hi, page_size, psk, psv);
+        issue_tile<D, DV>(ks_, ks_ + BN * SK, kbase, vbase, table, kt, k_lo, k_hi, page_size, page_shift, psk, psv);
         cp_async_commit();
     };
 

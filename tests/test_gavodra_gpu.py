@@ -228,7 +228,7 @@ def fill_pools(st, keys, vals, page, n_pages, dtype):
 
 
 ATTN_SHAPES = [(4, 2, 32, 16, 8), (3, 3, 8, 24, 16), (2, 1, 80, 40, 32), (6, 2, 64, 64, 16), (2, 1, 128, 32, 8),
-               (8, 2, 64, 32, 16), (4, 4, 128, 128, 16)]
+               (8, 2, 64, 32, 16), (4, 4, 128, 128, 16), (4, 2, 128, 64, 16), (2, 2, 64, 128, 32), (16, 1, 64, 64, 16)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
