@@ -624,12 +624,12 @@ def workload_lasapel(args, torch, np) -> dict:
 
 def gavodra_config(width: int, vocab: int = 32000) -> dict:
     """Four Gavodra layers at a real model's proportions: heads of 64 with four query heads a key head (as
-    the Llama layers beside them), a bias table of 32 rows reaching 128 positions back, one dense gated
+    the Llama layers beside them), a bias table of 48 rows reaching 128 positions back, one dense gated
     feed-forward of 8/3 widths and three routed ones (32 experts of half a width, 4 a token, beside a shared
     one of half a width: 2.5 widths of feed-forward a token)."""
     H = width // 64
     mix = {"heads": H, "kv_heads": max(1, H // 4), "dim": 64, "vdim": 64, "scale": 0.125, "bias_max": 128, "v_mix": True,
-           "bias_rows": 32}
+           "bias_rows": 48}
     moe = {"kind": "moe", "expert": {"ff": width // 2, "limit": 7.0}, "router": {"experts": 32, "top": 4, "scale": 2.5},
            "shared": {"ff": width // 2, "limit": 7.0}}
     dense = {"kind": "dense", "ff": width * 8 // 3 // 128 * 128, "limit": 7.0}

@@ -5,11 +5,19 @@
 
 namespace tc {
 
+// Parameters of the gated epilogue with clipping (EPI 3): g' sigmoid(slope g') (u' + shift) with g' = min(g,
+// limit) and u' = clamp(u, -limit, limit); limit +inf clips nothing.
+struct GluParams {
+    float slope, limit, shift;
+};
+
 // EPI 0: bf16 y [M, N].  EPI 1: SwiGLU over a gate|up matrix whose rows are interleaved in blocks of
 // 4 (columns 8 t .. 8 t + 3 gate, 8 t + 4 .. 8 t + 7 up), y [M, N / 2] bf16.  EPI 2: float32 y [M, N].
+// EPI 3: the layout of EPI 1 with the clipped gating of GluParams.
 // r: the sums of columns col .. col + 31 of row `row`; columns from N on are not stored.
 template <int EPI>
-__device__ __forceinline__ void store_sums32(const uint32_t (&r)[32], void* __restrict__ y, int row, int col, int N) {
+__device__ __forceinline__ void store_sums32(const uint32_t (&r)[32], void* __restrict__ y, int row, int col, int N,
+                                             const GluParams& gp) {
     if (EPI == 0) {
         bf16* o = reinterpret_cast<bf16*>(y) + (size_t)row * N + col;
 #pragma unroll
@@ -22,7 +30,7 @@ __device__ __forceinline__ void store_sums32(const uint32_t (&r)[32], void* __re
             pk.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
             *reinterpret_cast<uint4*>(o + v * 8) = pk;
         }
-    } else if (EPI == 1) {
+    } else if (EPI == 1 || EPI == 3) {
         bf16* o = reinterpret_cast<bf16*>(y) + (size_t)row * (N >> 1) + (col >> 1);
         float res[16];
 #pragma unroll
@@ -30,7 +38,12 @@ __device__ __forceinline__ void store_sums32(const uint32_t (&r)[32], void* __re
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float gt = __uint_as_float(r[tt * 8 + j]), up = __uint_as_float(r[tt * 8 + 4 + j]);
-                res[tt * 4 + j] = gt / (1.0f + expf(-gt)) * up;
+                if (EPI == 1) {
+                    res[tt * 4 + j] = gt / (1.0f + expf(-gt)) * up;
+                } else {
+                    const float g = fminf(gt, gp.limit), u = fminf(fmaxf(up, -gp.limit), gp.limit);
+                    res[tt * 4 + j] = g / (1.0f + expf(-gp.slope * g)) * (u + gp.shift);
+                }
             }
 #pragma unroll
         for (int v = 0; v < 2; ++v) {

@@ -45,7 +45,8 @@ struct Ctrl {
 
 constexpr uint32_t IDESC = idesc_bf16(BM, BN);
 
-// EPI 0: bf16 y [M, N].  EPI 1: SwiGLU, y [M, N / 2] bf16.  EPI 2: float32 y [M, N].
+// EPI 0: bf16 y [M, N].  EPI 1: SwiGLU, y [M, N / 2] bf16.  EPI 2: float32 y [M, N].  EPI 3: the gated epilogue
+// with a slope, a clipping limit and a shifted linear branch (gp), y [M, N / 2] bf16.
 // Persistent: CTA b works on tiles b, b + gridDim.x, ...; tile t -> (n tile t / m_tiles, m tile
 // t % m_tiles), so the CTAs that run together share a few column blocks of W and all of x in L2.
 // The accumulator is double-buffered in tensor memory (2 x 256 columns): the epilogue of a tile
@@ -54,7 +55,7 @@ template <int EPI>
 __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                   const __grid_constant__ CUtensorMap map_w,
                                                                   void* __restrict__ y, int M, int N, int K,
-                                                                  int m_tiles, int num_tiles) {
+                                                                  int m_tiles, int num_tiles, GluParams gp) {
     pdl_wait();
     extern __shared__ unsigned char gt_smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gt_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -139,7 +140,7 @@ __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_c
                 tmem_ld32(tmem_acc + (uint32_t)(cb * 32), r);
                 const int col = n0 + cb * 32;
                 if (!ok || row >= M || col >= N) continue;
-                store_sums32<EPI>(r, y, row, col, N);
+                store_sums32<EPI>(r, y, row, col, N, gp);
             }
             // this warp has read its lanes of the buffer: hand it back to the product warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -167,16 +168,16 @@ extern "C" int rlis_gemm_tcgen05_error(void) {
 extern "C" int* rlis_gemm_tcgen05_error_addr(void) { return tc::error_word_addr(); }
 
 // epilogue 0: bf16 y [M, N]; 1: SwiGLU (rows of W interleaved gate/up in blocks of 4), bf16 y [M, N / 2];
-// 2: float32 y [M, N].  K and N must be multiples of 8; pointers 16-byte aligned.
-extern "C" int rlis_gemm_tcgen05(const void* x, const void* W, void* y, int M, int N, int K, int epilogue,
-                                 cudaStream_t stream) {
+// 2: float32 y [M, N]; 3: as 1 with the gating of `gp`.  K and N must be multiples of 8; pointers 16-byte aligned.
+static int gemm_tcgen05_impl(const void* x, const void* W, void* y, int M, int N, int K, int epilogue, GluParams gp,
+                             cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || (K & 7) != 0 || (N & 7) != 0 || epilogue < 0 || epilogue > 2) return RLIS_ERR_UNSUPPORTED;
-    if (epilogue == 1 && (N & 15) != 0) return RLIS_ERR_UNSUPPORTED;   // rows of N / 2 bf16 must stay 16-byte aligned
+    if (K <= 0 || (K & 7) != 0 || (N & 7) != 0 || epilogue < 0 || epilogue > 3) return RLIS_ERR_UNSUPPORTED;
+    if ((epilogue == 1 || epilogue == 3) && (N & 15) != 0) return RLIS_ERR_UNSUPPORTED;   // rows of N / 2 bf16 must stay 16-byte aligned
     if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
         return RLIS_ERR_UNSUPPORTED;
     // more than one tile of rows: two SMs to a tile of 256 x 256
-    if (g_pair != 0 && M > BM) return launch_gemm_pair(x, W, y, M, N, K, epilogue, stream);
+    if (g_pair != 0 && M > BM) return launch_gemm_pair(x, W, y, M, N, K, epilogue, gp, stream);
     CUtensorMap map_x, map_w;
     if (!make_map(&map_x, x, M, K, BM) || !make_map(&map_w, W, N, K, BN)) return RLIS_ERR_UNSUPPORTED;
     static bool attr_done = false;
@@ -184,6 +185,7 @@ extern "C" int rlis_gemm_tcgen05(const void* x, const void* W, void* y, int M, i
         cudaFuncSetAttribute(gemm_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM);
         cudaFuncSetAttribute(gemm_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM);
         cudaFuncSetAttribute(gemm_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM);
+        cudaFuncSetAttribute(gemm_tcgen05_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM);
         attr_done = true;
     }
     const int m_tiles = (M + BM - 1) / BM, num_tiles = m_tiles * ((N + BN - 1) / BN);
@@ -191,10 +193,25 @@ extern "C" int rlis_gemm_tcgen05(const void* x, const void* W, void* y, int M, i
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
     if (epilogue == 0)
-        rlis_launch(gemm_tcgen05_kernel<0>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles);
+        rlis_launch(gemm_tcgen05_kernel<0>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
     else if (epilogue == 1)
-        rlis_launch(gemm_tcgen05_kernel<1>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles);
+        rlis_launch(gemm_tcgen05_kernel<1>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
+    else if (epilogue == 2)
+        rlis_launch(gemm_tcgen05_kernel<2>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
     else
-        rlis_launch(gemm_tcgen05_kernel<2>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles);
+        rlis_launch(gemm_tcgen05_kernel<3>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
     return RLIS_LAUNCH_CHECK();
+}
+
+extern "C" int rlis_gemm_tcgen05(const void* x, const void* W, void* y, int M, int N, int K, int epilogue,
+                                 cudaStream_t stream) {
+    if (epilogue < 0 || epilogue > 2) return RLIS_ERR_UNSUPPORTED;
+    return gemm_tcgen05_impl(x, W, y, M, N, K, epilogue, GluParams{1.0f, INFINITY, 0.0f}, stream);
+}
+
+// The gate|up product with the clipped gating in its epilogue: W's rows interleaved gate/up in blocks of 4,
+// y [M, N / 2] bf16 = g' sigmoid(slope g') (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit).
+extern "C" int rlis_gemm_tcgen05_glu(const void* x, const void* W, void* y, int M, int N, int K, float slope,
+                                     float limit, float shift, cudaStream_t stream) {
+    return gemm_tcgen05_impl(x, W, y, M, N, K, 3, GluParams{slope, limit, shift}, stream);
 }

@@ -90,7 +90,7 @@ template <int EPI>
 __global__ __launch_bounds__(GP_THREADS) void gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                        const __grid_constant__ CUtensorMap map_w,
                                                                        void* __restrict__ y, int M, int N, int K,
-                                                                       int m_tiles, int num_tiles) {
+                                                                       int m_tiles, int num_tiles, GluParams gp) {
     pdl_wait();
     extern __shared__ unsigned char gp_smem_raw[];
     // the same offset in both CTAs (their dynamic arrays start at the same address): the instruction
@@ -196,7 +196,7 @@ __global__ __launch_bounds__(GP_THREADS) void gemm_tcgen05_pair_kernel(const __g
                 tmem_ld32(tmem_acc + (uint32_t)(cb * 32), r);
                 const int col = n0 + cb * 32;
                 if (!ok || row >= M || col >= N) continue;
-                store_sums32<EPI>(r, y, row, col, N);
+                store_sums32<EPI>(r, y, row, col, N, gp);
             }
             // this warp has read its lanes of the buffer: CTA 0's product warp may write it again
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -221,7 +221,8 @@ int g_pair = -1;        // -1: where the tiles allow; 0: never (measurements)
 extern "C" void rlis_gemm_tcgen05_set_pair(int on) { g_pair = on; }
 
 // The same contract as rlis_gemm_tcgen05.// (the caller has checked the sizes and the alignment)
-static int launch_gemm_pair(const void* x, const void* W, void* y, int M, int N, int K, int epilogue, cudaStream_t stream) {
+static int launch_gemm_pair(const void* x, const void* W, void* y, int M, int N, int K, int epilogue, GluParams gp,
+                            cudaStream_t stream) {
     CUtensorMap map_x, map_w;
     if (!make_map(&map_x, x, M, K, PM) || !make_map(&map_w, W, N, K, PN / 2)) return RLIS_ERR_UNSUPPORTED;
     static bool attr_done = false;
@@ -229,6 +230,7 @@ static int launch_gemm_pair(const void* x, const void* W, void* y, int M, int N,
         cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GP_SMEM);
         cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GP_SMEM);
         cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GP_SMEM);
+        cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GP_SMEM);
         attr_done = true;
     }
     const int m_tiles = (M + 2 * PM - 1) / (2 * PM), num_tiles = m_tiles * ((N + PN - 1) / PN);
@@ -238,10 +240,12 @@ static int launch_gemm_pair(const void* x, const void* W, void* y, int M, int N,
     const unsigned grid = (unsigned)(2 * pairs);
     const dim3 cluster(2, 1, 1);
     if (epilogue == 0)
-        rlis_launch_cluster(gemm_tcgen05_pair_kernel<0>, dim3(grid), dim3(GP_THREADS), GP_SMEM, stream, cluster, map_x, map_w, y, M, N, K, m_tiles, num_tiles);
+        rlis_launch_cluster(gemm_tcgen05_pair_kernel<0>, dim3(grid), dim3(GP_THREADS), GP_SMEM, stream, cluster, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
     else if (epilogue == 1)
-        rlis_launch_cluster(gemm_tcgen05_pair_kernel<1>, dim3(grid), dim3(GP_THREADS), GP_SMEM, stream, cluster, map_x, map_w, y, M, N, K, m_tiles, num_tiles);
+        rlis_launch_cluster(gemm_tcgen05_pair_kernel<1>, dim3(grid), dim3(GP_THREADS), GP_SMEM, stream, cluster, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
+    else if (epilogue == 2)
+        rlis_launch_cluster(gemm_tcgen05_pair_kernel<2>, dim3(grid), dim3(GP_THREADS), GP_SMEM, stream, cluster, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
     else
-        rlis_launch_cluster(gemm_tcgen05_pair_kernel<2>, dim3(grid), dim3(GP_THREADS), GP_SMEM, stream, cluster, map_x, map_w, y, M, N, K, m_tiles, num_tiles);
+        rlis_launch_cluster(gemm_tcgen05_pair_kernel<3>, dim3(grid), dim3(GP_THREADS), GP_SMEM, stream, cluster, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
     return RLIS_LAUNCH_CHECK();
 }

@@ -254,16 +254,20 @@ __global__ __launch_bounds__(256) void moe_combine_kernel(
     }
 }
 
+// interleave 0: gate in columns 0..I-1 and the linear branch in I..2I-1; interleave B > 0: blocks of B gate
+// columns followed by their B columns of the linear branch (the layout the products' gated epilogues want).
 template <typename T>
 __global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total,
-                               float slope, float limit, float shift) {
+                               float slope, float limit, float shift, int interleave) {
     pdl_wait_and_trigger();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / inter;
     const int i = (int)(idx - t * inter);
-    const float g = fminf(to_f<T>(gu[t * 2 * inter + i]), limit);
-    const float u = fminf(fmaxf(to_f<T>(gu[t * 2 * inter + inter + i]), -limit), limit);
+    const size_t gi = interleave > 0 ? (size_t)(i / interleave) * 2 * interleave + i % interleave : (size_t)i;
+    const size_t ui = interleave > 0 ? gi + interleave : (size_t)inter + i;
+    const float g = fminf(to_f<T>(gu[t * 2 * inter + gi]), limit);
+    const float u = fminf(fmaxf(to_f<T>(gu[t * 2 * inter + ui]), -limit), limit);
     out[idx] = from_f<T>(g * sigmoidf_(slope * g) * (u + shift));
 }
 }  // namespace
@@ -337,16 +341,17 @@ extern "C" int rlis_moe_combine(const float* y, const int* pair_slot, const floa
     return RLIS_LAUNCH_CHECK();
 }
 
-// out[t, i] = glu(gu[t, i], gu[t, inter + i]); limit +inf: no clipping.
+// out[t, i] = glu(gate column i, linear column i of gu[t, :]); limit +inf: no clipping.
 extern "C" int rlis_glu_act(const void* gu, void* out, int n_tokens, int inter, float slope, float limit, float shift,
-                            int dtype, cudaStream_t stream) {
+                            int interleave, int dtype, cudaStream_t stream) {
     const size_t total = (size_t)n_tokens * inter;
     if (total == 0) return 0;
+    if (interleave < 0 || (interleave > 0 && inter % interleave != 0)) return RLIS_ERR_UNSUPPORTED;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == RLIS_F32)
-        rlis_launch(glu_act_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, inter, total, slope, limit, shift);
+        rlis_launch(glu_act_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, inter, total, slope, limit, shift, interleave);
     else if (dtype == RLIS_BF16)
-        rlis_launch(glu_act_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, (bf16*)out, inter, total, slope, limit, shift);
+        rlis_launch(glu_act_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, (bf16*)out, inter, total, slope, limit, shift, interleave);
     else
         return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();

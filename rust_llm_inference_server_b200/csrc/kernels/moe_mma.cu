@@ -148,7 +148,7 @@ int launch(const void* A, const void* Wg, const void* Wu, void* out, const int* 
 }
 }  // namespace
 
-// The contract of rlis_moe_gemm (moe.cu) for bfloat16 operands whose k extent is a multiple of 8 and row
+// The arguments of rlis_moe_gemm (moe.cu), for bfloat16 operands whose k extent is a multiple of 8 and row
 // tiles of 32 or 128 slots.
 extern "C" int rlis_moe_gemm_mma(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair,
                                  const int* tile_expert, int max_tiles, int tile_rows, int top, int N, int K, int glu,

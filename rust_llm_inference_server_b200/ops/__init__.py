@@ -557,22 +557,30 @@ def stream_gemm(x, w: torch.Tensor, out_dtype=torch.bfloat16, swiglu4: bool = Fa
     return ScaledRows(xn, partials, N, sink.eps)
 
 
-def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epilogue: str = "plain") -> torch.Tensor:
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epilogue: str = "plain", glu: tuple | None = None) -> torch.Tensor:
     """y = x @ w^T on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory), bfloat16
     operands.  epilogue "plain": bf16 [M, N]; "float32": float32 [M, N]; "swiglu4": w is a gate|up
-    matrix interleaved in blocks of 4 rows and the result is silu(gate) * up, bf16 [M, N / 2]."""
+    matrix interleaved in blocks of 4 rows and the result is silu(gate) * up, bf16 [M, N / 2]; "glu4":
+    the same layout with the gating of `glu` = (slope, limit or None, up_shift), see `glu_act`."""
     M, K = x.shape
     N = w.shape[0]
     _req(x, "x", torch.bfloat16)
     _req(w, "w", torch.bfloat16, (N, K))
-    code = {"plain": 0, "swiglu4": 1, "float32": 2}[epilogue]
-    if M < 128 or N < 256 or K % 8 or N % (16 if code == 1 else 8):
+    code = {"plain": 0, "swiglu4": 1, "float32": 2, "glu4": 3}[epilogue]
+    gated = code in (1, 3)
+    if M < 128 or N < 256 or K % 8 or N % (16 if gated else 8):
         raise KernelError(f"gemm_tcgen05: takes M >= 128, N >= 256, K a multiple of 8 and N a multiple of 8 "
-                          f"(16 with the SwiGLU epilogue); got M={M}, N={N}, K={K}")
-    out = torch.empty((M, N // 2 if code == 1 else N), dtype=torch.float32 if code == 2 else torch.bfloat16,
+                          f"(16 with a gated epilogue); got M={M}, N={N}, K={K}")
+    out = torch.empty((M, N // 2 if gated else N), dtype=torch.float32 if code == 2 else torch.bfloat16,
                       device=x.device)
-    check(lib().rlis_gemm_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, code, _stream()),
-          "gemm_tcgen05")
+    if code == 3:
+        slope, limit, shift = glu
+        check(lib().rlis_gemm_tcgen05_glu(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, float(slope),
+                                          float("inf") if limit is None else float(limit), float(shift), _stream()),
+              "gemm_tcgen05")
+    else:
+        check(lib().rlis_gemm_tcgen05(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, code, _stream()),
+              "gemm_tcgen05")
     _count("gemm_tcgen05." + epilogue)
     return out
 
@@ -948,17 +956,18 @@ def attention(q, k_cache, v_cache, out, step, group: int, n_heads: int, n_kv_hea
 
 
 def glu_act(gate_up: torch.Tensor, out: torch.Tensor, slope: float = 1.0, limit: float | None = None,
-            up_shift: float = 0.0) -> torch.Tensor:
+            up_shift: float = 0.0, interleave: int = 0) -> torch.Tensor:
     """out[t, i] = g sigmoid(slope g) (u + up_shift) with g = gate_up[t, i] and u = gate_up[t, I + i], both in
-    float32; with a `limit`, g is cut at limit from above and u clipped to [-limit, limit] first."""
+    float32; with a `limit`, g is cut at limit from above and u clipped to [-limit, limit] first.
+    interleave B > 0: blocks of B gate columns each followed by their B columns of u."""
     T, I2 = gate_up.shape
     if I2 % 2:
         raise KernelError(f"glu_act: the stacked gate|up width must be even, got {I2}")
     _req(gate_up, "gate_up")
     _req(out, "out", gate_up.dtype, (T, I2 // 2))
     check(lib().rlis_glu_act(gate_up.data_ptr(), out.data_ptr(), T, I2 // 2, float(slope),
-                             float("inf") if limit is None else float(limit), float(up_shift), _code(out.dtype),
-                             _stream()), "glu_act")
+                             float("inf") if limit is None else float(limit), float(up_shift), int(interleave),
+                             _code(out.dtype), _stream()), "glu_act")
     _count("glu_act")
     return out
 

@@ -50,7 +50,7 @@ SIGNATURES = {
     "rlis_moe_gemm_mma": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, P],
     "rlis_moe_mma_takes_tile": [I],
     "rlis_moe_combine": [P, P, P, P, P, P, I, I, I, I, P],
-    "rlis_glu_act": [P, P, I, I, F, F, F, I, P],
+    "rlis_glu_act": [P, P, I, I, F, F, F, I, I, P],
     "rlis_rope_cache": [P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "rlis_attention_generic": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P],
     "rlis_attention_decode": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
@@ -64,6 +64,7 @@ SIGNATURES = {
     "rlis_sample_filtered": [P, P, P, I, I, LL, P],
     "rlis_nll_rows": [P, P, P, I, I, LL, P],
     "rlis_gemm_tcgen05": [P, P, P, I, I, I, I, P],
+    "rlis_gemm_tcgen05_glu": [P, P, P, I, I, I, F, F, F, P],
     "rlis_stream_gemm_bf16": [P, P, P, I, I, I, I, I, P],
     "rlis_stream_gemm_fused": [P, P, P, I, I, I, I, I, P, I, I, F, P, P, P, P, P],
     "rlis_take_errors": [P, P],

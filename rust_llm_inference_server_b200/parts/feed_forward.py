@@ -34,7 +34,7 @@ class SwiGLU(FeedForward):
     def load(self, src) -> None:
         s = self.spec
         g, u = src.get(s.gate_proj), src.get(s.up_proj)
-        self.interleave = 4 if s.intermediate % 4 == 0 and self.plain else 0
+        self.interleave = 4 if s.intermediate % 4 == 0 else 0
         if self.interleave:
             self.w_gate_up = torch.stack([g.view(-1, 4, s.hidden), u.view(-1, 4, s.hidden)], dim=1) \
                 .reshape(2 * s.intermediate, s.hidden).contiguous()
@@ -48,11 +48,17 @@ class SwiGLU(FeedForward):
     def forward(self, x, step, sink=None):
         if not self.plain:
             s = self.spec
-            with span("mlp gate+up"):
-                gu = ops.linear(x, self.w_gate_up)
-            with span("clipped gating"):
-                act = step.buffer("ffn_act", (x.shape[0], s.intermediate), self.dtype)
-                ops.glu_act(gu, act, s.slope, s.limit, s.up_shift)
+            if (self.dtype == torch.bfloat16 and self.interleave == 4 and s.hidden % 8 == 0 and x.shape[0] >= 128
+                    and s.intermediate % 128 == 0):
+                # prefill: the tcgen05 product with the clipped gating in its epilogue
+                with span("mlp gate+up, clipped gating"):
+                    act = ops.gemm_tcgen05(x, self.w_gate_up, "glu4", glu=(s.slope, s.limit, s.up_shift))
+            else:
+                with span("mlp gate+up"):
+                    gu = ops.linear(x, self.w_gate_up)
+                with span("clipped gating"):
+                    act = step.buffer("ffn_act", (x.shape[0], s.intermediate), self.dtype)
+                    ops.glu_act(gu, act, s.slope, s.limit, s.up_shift, self.interleave)
             with span("mlp down proj"):
                 return ops.linear(act, self.w_down)
         fusable = self.dtype == torch.bfloat16 and self.interleave == 4 and self.spec.hidden % 8 == 0

@@ -65,7 +65,7 @@ CONFIGS = {
     ]),
     # head sizes that the tensor-core kernels take: 64 / 64 with three heads a group, 128 / 32 with one group
     "C": model(157, 128, 1e-5, [
-        layer(attn(6, 2, 64, 64, 0.11, 90.0), dense(96, 2.0)),
+        layer(attn(6, 2, 64, 64, 0.11, 90.0), dense(128, 2.0)),      # a feed-forward the product with the gated epilogue takes
         layer(attn(2, 1, 128, 32, 0.07, 300.0, v_mix=False), moe(6, 2, 32, 1.2, 2.0, shared=(48, 0.9))),
         layer(attn(4, 2, 128, 64, 0.06, 50.0)),
     ], residual_mult=0.5, emb_scale=2.0, logit_scale=0.6, softcap=20.0),

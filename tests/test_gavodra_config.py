@@ -138,3 +138,29 @@ def test_a_missing_mechanism_shows_in_the_logits(which):
     # a limit that is not applied; a wrong scale
     assert moved(cfg_edit=lambda c: [l["mlp"].update(limit=50.0) for l in c["layers"] if l["mlp"] and l["mlp"]["kind"] == "dense"]) > 0.05
     assert moved(cfg_edit=lambda c: c["layers"][0]["mixer"].update(scale=c["layers"][0]["mixer"]["scale"] * 2)) > 0.2
+
+
+def test_value_rows_of_their_own_width_get_a_pool_of_their_own():
+    """Sizing counts key and value rows by their own widths, and equal specs still share a group."""
+    from rust_llm_inference_server_b200.cache.storage import plan_groups, size_groups
+    from rust_llm_inference_server_b200.parts.base import KVCacheSpec
+    narrow = KVCacheSpec(2, 64, None, v_head_dim=16)
+    same = KVCacheSpec(2, 64, None)
+    groups = plan_groups([narrow, same, narrow, None, same], 8)
+    assert [g.slots for g in groups] == [[0, 2], [1, 4]]
+    assert groups[0].bytes_per_page(2) == 2 * 2 * 8 * (64 + 16) * 2 and groups[0].v_head_dim == 16
+    assert groups[1].bytes_per_page(2) == 2 * 2 * 8 * (64 + 64) * 2 and groups[1].v_head_dim == 64
+    size_groups(groups, 10 * (groups[0].bytes_per_page(2) + groups[1].bytes_per_page(2)), 2)
+    assert [g.num_pages for g in groups] == [10, 10]
+
+
+def test_a_checkpoint_may_decide_an_open_extent():
+    import torch
+    from rust_llm_inference_server_b200.weights.loader import WeightError, check_checkpoint
+    from rust_llm_inference_server_b200.weights.safetensors_io import Checkpoint
+    ckpt = Checkpoint(tensors={"t": torch.zeros(7, 3), "u": torch.zeros(2)})
+    check_checkpoint({"t": (None, 3), "u": (2,)}, ckpt)
+    with pytest.raises(WeightError):
+        check_checkpoint({"t": (None, 4), "u": (2,)}, ckpt)
+    with pytest.raises(WeightError):
+        check_checkpoint({"t": (None,), "u": (2,)}, ckpt)

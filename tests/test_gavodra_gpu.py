@@ -228,7 +228,7 @@ def fill_pools(st, keys, vals, page, n_pages, dtype):
 
 
 ATTN_SHAPES = [(4, 2, 32, 16, 8), (3, 3, 8, 24, 16), (2, 1, 80, 40, 32), (6, 2, 64, 64, 16), (2, 1, 128, 32, 8),
-               (8, 2, 64, 32, 16), (4, 4, 128, 128, 16), (4, 2, 128, 64, 16), (2, 2, 64, 128, 32), (16, 1, 64, 64, 16)]
+               (8, 4, 64, 32, 16), (4, 4, 128, 128, 16), (4, 2, 128, 64, 16), (2, 2, 64, 128, 32), (16, 1, 64, 64, 16)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -286,7 +286,7 @@ def test_attention_far_keys_table_rows_page_borders_and_gates(dtype, H, G, d, dv
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,E,top,W,I", [(1, 3, 1, 40, 24), (37, 5, 2, 96, 40), (150, 8, 3, 64, 72), (64, 4, 4, 32, 16),
+@pytest.mark.parametrize("T,E,top,W,I", [(1, 3, 1, 40, 24), (37, 5, 2, 96, 40), (150, 9, 3, 64, 72), (64, 4, 4, 32, 16),
                                           (300, 3, 2, 64, 48)])         # the last: wide tiles of the sort
 def test_routing_choice_sort_and_experts(dtype, T, E, top, W, I):
     from rust_llm_inference_server_b200 import ops
@@ -325,6 +325,30 @@ def test_routing_choice_sort_and_experts(dtype, T, E, top, W, I):
     plan = ops.moe_route(x, wr[:E].contiguous(), None, E, top, 1.0, False, st)
     assert plan.shared_gate is None
     assert np.array_equal(plan.top_idx.view(T, top).cpu().numpy(), P.route(host(x), host(wr)[:E], np.zeros(E), top, 1.0)[0])
+
+
+def test_gated_product_with_clipping_in_its_epilogue():
+    """The tcgen05 gate|up product with the clipped gating on its accumulators against the plain form, one
+    tile of rows (one SM a tile) and several (two SMs a tile), and the gating kernel on the same layout."""
+    from rust_llm_inference_server_b200 import ops
+    rng = np.random.default_rng(2)
+    K, I = 96, 256
+    wg, wu = rng.standard_normal((I, K)) / np.sqrt(K) * 2, rng.standard_normal((I, K)) / np.sqrt(K) * 2
+    w = torch.stack([dev(wg, torch.bfloat16).view(-1, 4, K), dev(wu, torch.bfloat16).view(-1, 4, K)], dim=1).reshape(2 * I, K).contiguous()
+    for M in (128, 300):
+        x = dev(rng.standard_normal((M, K)), torch.bfloat16)
+        for slope, limit, shift in ((1.702, 0.8, 1.0), (1.0, None, 0.0)):
+            got = ops.gemm_tcgen05(x, w, "glu4", glu=(slope, limit, shift))
+            g, u = host(x) @ host(dev(wg, torch.bfloat16)).T, host(x) @ host(dev(wu, torch.bfloat16)).T
+            if limit is not None:
+                g, u = np.minimum(g, limit), np.clip(u, -limit, limit)
+            want = g * P.sigmoid(slope * g) * (u + shift)
+            np.testing.assert_allclose(host(got), want, rtol=0.01, atol=0.02)     # one rounding to bfloat16
+            gu = ops.linear(x, w)
+            out = torch.empty((M, I), dtype=torch.bfloat16, device="cuda")
+            ops.glu_act(gu, out, slope, limit, shift, 4)
+            np.testing.assert_allclose(host(out), want, rtol=0.02, atol=0.03)     # the sums are rounded before the gating here
+    ops.check_device_errors()
 
 
 # ---- whole models ------------------------------------------------------------------------------
@@ -387,7 +411,7 @@ def test_all_ways_of_cutting_give_the_plain_logits(model_root, which, page, lens
         worst, where = worst_difference(results[fam], whole)
         assert worst <= TOL_BETWEEN[dtype], f"{which} {dtype}: {fam} differs from whole by {worst} at {where}"
     fast = dtype == "bfloat16" and which == "C"
-    for k in (("attention_bias.decode.mma", "attention_bias.prefill.mma") if fast else ("attention_bias",)) + \
+    for k in (("attention_bias.decode.mma", "attention_bias.prefill.mma", "gemm_tcgen05.glu4") if fast else ("attention_bias",)) + \
             (("moe_gemm.mma.glu", "moe_gemm.mma.down") if dtype == "bfloat16" and which != "D" else ("moe_gemm.glu", "moe_gemm.down")) + \
             ("qk_norm_store", "qk_norm_store.mix", "post_norm_residual", "post_norm_residual.copy" if dtype == "bfloat16" else
               "post_norm_residual", "glu_act", "moe_route", "moe_align", "moe_combine"):
