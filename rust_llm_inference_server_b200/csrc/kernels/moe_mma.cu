@@ -1,7 +1,8 @@
 // The routed feed-forward's two products on the tensor cores (bfloat16; moe.cu describes the layer and
 // holds the float32 products).  A tile of TM slots (32, or 128 when there are many pairs an expert)
 // belongs to one expert (the sort pads every expert's run); a CTA forms TM slots x 64 features of it
-// with mma.sync m16n8k16 and float32 sums, a warp 16 slots x 32 features.  Operands arrive by 16-byte
+// with mma.sync m16n8k16 and float32 sums, a warp 16 slots x 32 features (32 x 32 in the wide tiles, where
+// a fragment of the weights then serves two of the slots' fragments).  Operands arrive by 16-byte
 // asynchronous copies in steps of 64 along k through three stages, so two steps of weights are in
 // flight while one is multiplied: with a few tokens a step the products are a stream of expert weights
 // and live on bytes in flight.  The first product gathers its rows by token and forms gate and linear
@@ -17,11 +18,12 @@ constexpr int TN = 64, TK = 64, SA = TK + 8, STAGES = 3;
 template <bool GLU, int TM> struct MoeSmem { static constexpr int STAGE = (TM + TN * (GLU ? 2 : 1)) * SA; };
 
 template <bool GLU, int TM>
-__global__ __launch_bounds__(TM * 4) void moe_mma_kernel(
+__global__ __launch_bounds__(TM == 128 ? 256 : TM * 4) void moe_mma_kernel(
     const bf16* __restrict__ A, const bf16* __restrict__ Wg, const bf16* __restrict__ Wu, void* __restrict__ out_,
     const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert, int top, int N, int K,
     float slope, float limit, float shift) {
-    constexpr int THREADS = TM * 4;                  // TM / 16 x 2 warps
+    constexpr int MT = TM == 128 ? 2 : 1;            // fragments of 16 slots a warp
+    constexpr int THREADS = TM * 4 / MT;             // TM / (16 MT) x 2 warps
     constexpr int STAGE = MoeSmem<GLU, TM>::STAGE;
     pdl_wait();
     const int e = tile_expert[blockIdx.y];
@@ -38,7 +40,7 @@ __global__ __launch_bounds__(TM * 4) void moe_mma_kernel(
     const bf16* wg = Wg + (size_t)e * N * K;
     const bf16* wu = GLU ? Wu + (size_t)e * N * K : nullptr;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int wm = warp >> 1, wn = warp & 1;         // a warp: 16 slots x 32 features
+    const int wm = warp >> 1, wn = warp & 1;         // a warp: 16 MT slots x 32 features
     const int g = lane >> 2, c = lane & 3;
 
     auto issue = [&](int k0, int st) {
@@ -68,11 +70,13 @@ __global__ __launch_bounds__(TM * 4) void moe_mma_kernel(
         cp_async_commit();
     };
 
-    float accg[4][4], accu[4][4];
+    float accg[MT][4][4], accu[MT][4][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int m = 0; m < MT; ++m)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) accg[i][j] = accu[i][j] = 0.f;
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) accg[m][i][j] = accu[m][i][j] = 0.f;
 
     const int nk = (K + TK - 1) / TK;
 #pragma unroll
@@ -88,30 +92,39 @@ __global__ __launch_bounds__(TM * 4) void moe_mma_kernel(
         const bf16* as = sm + (size_t)(kt % STAGES) * STAGE;
         const bf16* gs = as + TM * SA;
         const bf16* us = gs + TN * SA;
-        uint32_t a[4][4];
+        uint32_t a[MT][4][4];
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-            ldmatrix_x4(a[kk], as + (wm * 16 + (lane & 15)) * SA + kk * 16 + (lane >> 4) * 8);
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+                ldmatrix_x4(a[m][kk], as + ((wm * MT + m) * 16 + (lane & 15)) * SA + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
             for (int k2 = 0; k2 < 2; ++k2) {
                 uint32_t b[4];
                 ldmatrix_x4(b, gs + (wn * 32 + nt * 8 + (lane & 7)) * SA + k2 * 32 + (lane >> 3) * 8);
-                mma_bf16_16816(accg[nt], a[2 * k2], b[0], b[1]);
-                mma_bf16_16816(accg[nt], a[2 * k2 + 1], b[2], b[3]);
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    mma_bf16_16816(accg[m][nt], a[m][2 * k2], b[0], b[1]);
+                    mma_bf16_16816(accg[m][nt], a[m][2 * k2 + 1], b[2], b[3]);
+                }
                 if (GLU) {
                     ldmatrix_x4(b, us + (wn * 32 + nt * 8 + (lane & 7)) * SA + k2 * 32 + (lane >> 3) * 8);
-                    mma_bf16_16816(accu[nt], a[2 * k2], b[0], b[1]);
-                    mma_bf16_16816(accu[nt], a[2 * k2 + 1], b[2], b[3]);
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        mma_bf16_16816(accu[m][nt], a[m][2 * k2], b[0], b[1]);
+                        mma_bf16_16816(accu[m][nt], a[m][2 * k2 + 1], b[2], b[3]);
+                    }
                 }
             }
     }
     cp_async_wait<0>();
     pdl_trigger();
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int r = wm * 16 + g + half * 8;
+    for (int mh = 0; mh < 2 * MT; ++mh) {
+        const int m = mh >> 1, half = mh & 1;
+        const int r = (wm * MT + m) * 16 + g + half * 8;
         if (rows[r] < 0) continue;
         const size_t orow = (size_t)(slot0 + r) * N;
 #pragma unroll
@@ -120,10 +133,10 @@ __global__ __launch_bounds__(TM * 4) void moe_mma_kernel(
             for (int j = 0; j < 2; ++j) {
                 const int gn = n0 + wn * 32 + nt * 8 + 2 * c + j;
                 if (gn >= N) continue;
-                const float vg = accg[nt][half * 2 + j];
+                const float vg = accg[m][nt][half * 2 + j];
                 if (GLU) {
                     const float gg = fminf(vg, limit);
-                    const float uu = fminf(fmaxf(accu[nt][half * 2 + j], -limit), limit);
+                    const float uu = fminf(fmaxf(accu[m][nt][half * 2 + j], -limit), limit);
                     ((bf16*)out_)[orow + gn] = __float2bfloat16_rn(gg / (1.0f + expf(-slope * gg)) * (uu + shift));
                 } else {
                     ((float*)out_)[orow + gn] = vg;
@@ -142,7 +155,7 @@ int launch(const void* A, const void* Wg, const void* Wu, void* out, const int* 
         raised = true;
     }
     dim3 grid((N + TN - 1) / TN, max_tiles);
-    rlis_launch(moe_mma_kernel<GLU, TM>, grid, TM * 4, smem, stream, (const bf16*)A, (const bf16*)Wg, (const bf16*)Wu, out,
+    rlis_launch(moe_mma_kernel<GLU, TM>, grid, TM == 128 ? 256 : TM * 4, smem, stream, (const bf16*)A, (const bf16*)Wg, (const bf16*)Wu, out,
                 sorted_pair, tile_expert, top, N, K, slope, limit, shift);
     return RLIS_LAUNCH_CHECK();
 }
