@@ -24,6 +24,15 @@ constexpr int BM = 32, BN = 64, BK = 16;     // the FFMA product's own tile; a r
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 
+// Four consecutive elements (from an address aligned to four of them) as floats, in one load.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
 // A CTA takes TOK tokens and has a warp for every row of W_r (up to 32 warps): a warp forms its row against
 // all of the CTA's tokens, so the matrix is read once a CTA (the tokens' rows come back from the first-level
 // cache) and the rows' sums run side by side; then one warp a token chooses.
@@ -51,11 +60,11 @@ __global__ __launch_bounds__(1024) void moe_route_kernel(
 #pragma unroll
                 for (int i = 0; i < TOK; ++i) {
                     const int t = min(t0 + i, n_tokens - 1);
-                    const T* xr = x + (size_t)t * width + k;
-                    dot[i] = fmaf(wv.x, to_f<T>(xr[0]), dot[i]);
-                    dot[i] = fmaf(wv.y, to_f<T>(xr[1]), dot[i]);
-                    dot[i] = fmaf(wv.z, to_f<T>(xr[2]), dot[i]);
-                    dot[i] = fmaf(wv.w, to_f<T>(xr[3]), dot[i]);
+                    const float4 xv = load4(x + (size_t)t * width + k);
+                    dot[i] = fmaf(wv.x, xv.x, dot[i]);
+                    dot[i] = fmaf(wv.y, xv.y, dot[i]);
+                    dot[i] = fmaf(wv.z, xv.z, dot[i]);
+                    dot[i] = fmaf(wv.w, xv.w, dot[i]);
                 }
             }
         } else {
