@@ -51,11 +51,14 @@ constexpr uint32_t IDESC = idesc_bf16(BM, BN);
 // t % m_tiles), so the CTAs that run together share a few column blocks of W and all of x in L2.
 // The accumulator is double-buffered in tensor memory (2 x 256 columns): the epilogue of a tile
 // overlaps the products of the next one.
+// Grouped form (tile_expert given): row tile m of x belongs to expert tile_expert[m] (or to none: -1, the
+// tile is left out by every warp alike), whose N rows of W start at row expert * expert_rows of the map.
 template <int EPI>
 __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                   const __grid_constant__ CUtensorMap map_w,
                                                                   void* __restrict__ y, int M, int N, int K,
-                                                                  int m_tiles, int num_tiles, GluParams gp) {
+                                                                  int m_tiles, int num_tiles, GluParams gp,
+                                                                  const int* __restrict__ tile_expert, int expert_rows) {
     pdl_wait();
     extern __shared__ unsigned char gt_smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gt_smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -92,19 +95,26 @@ __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_c
             int it = 0;
             for (int tile = blockIdx.x; tile < num_tiles && !ctrl->abort; tile += gridDim.x) {
                 const int n0 = (tile / m_tiles) * BN, m0 = (tile % m_tiles) * BM;
+                int w_row = n0;
+                if (tile_expert != nullptr) {
+                    const int e = tile_expert[tile % m_tiles];
+                    if (e < 0) continue;
+                    w_row += e * expert_rows;
+                }
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !bar_wait(&ctrl->empty[s], ((it / STAGES) - 1) & 1, &ctrl->abort)) break;
                     bar_expect_tx(&ctrl->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
                     tma_load_2d(a_tiles + (size_t)s * A_STAGE_BYTES, &map_x, kb * BK, m0, &ctrl->full[s]);
-                    tma_load_2d(b_tiles + (size_t)s * B_STAGE_BYTES, &map_w, kb * BK, n0, &ctrl->full[s]);
+                    tma_load_2d(b_tiles + (size_t)s * B_STAGE_BYTES, &map_w, kb * BK, w_row, &ctrl->full[s]);
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            int it = 0, t = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && !ctrl->abort; tile += gridDim.x, ++t) {
+            int it = 0, t = 0;      // t counts the tiles this CTA works on (a tile that is left out is not one)
+            for (int tile = blockIdx.x; tile < num_tiles && !ctrl->abort; tile += gridDim.x) {
+                if (tile_expert != nullptr && tile_expert[tile % m_tiles] < 0) continue;
                 const int buf = t & 1;
                 if (t >= 2 && !bar_wait(&ctrl->acc_empty[buf], ((t >> 1) - 1) & 1, &ctrl->abort)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -122,13 +132,15 @@ __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_c
                     umma_commit(&ctrl->empty[s]);              // the stage is free once these products are done
                 }
                 umma_commit(&ctrl->acc_full[buf]);
+                ++t;
             }
         }
     } else {
         // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
         const int q = warp & 3;
         int t = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            if (tile_expert != nullptr && tile_expert[tile % m_tiles] < 0) continue;
             const int buf = t & 1;
             const int n0 = (tile / m_tiles) * BN, m0 = (tile % m_tiles) * BM;
             const bool ok = bar_wait(&ctrl->acc_full[buf], (t >> 1) & 1, &ctrl->abort);
@@ -146,6 +158,7 @@ __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_c
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) bar_arrive(&ctrl->acc_empty[buf]);
+            ++t;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -193,13 +206,46 @@ static int gemm_tcgen05_impl(const void* x, const void* W, void* y, int M, int N
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
     if (epilogue == 0)
-        rlis_launch(gemm_tcgen05_kernel<0>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
+        rlis_launch(gemm_tcgen05_kernel<0>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp, (const int*)nullptr, 0);
     else if (epilogue == 1)
-        rlis_launch(gemm_tcgen05_kernel<1>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
+        rlis_launch(gemm_tcgen05_kernel<1>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp, (const int*)nullptr, 0);
     else if (epilogue == 2)
-        rlis_launch(gemm_tcgen05_kernel<2>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
+        rlis_launch(gemm_tcgen05_kernel<2>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp, (const int*)nullptr, 0);
     else
-        rlis_launch(gemm_tcgen05_kernel<3>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp);
+        rlis_launch(gemm_tcgen05_kernel<3>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp, (const int*)nullptr, 0);
+    return RLIS_LAUNCH_CHECK();
+}
+
+// Grouped form: x [M, K] in row tiles of 128 (M a multiple of 128), row tile m multiplied by expert
+// tile_expert[m]'s matrix W[e] [N, K] of W [n_experts, N, K] (-1: the tile is left out); epilogue 0 (bf16
+// y [M, N]) or 2 (float32).  One SM a tile.  tile_expert is read on the device: nothing of it reaches the host.
+extern "C" int rlis_gemm_tcgen05_grouped(const void* x, const void* W, void* y, int M, int N, int K, int n_experts,
+                                         const int* tile_expert, int epilogue, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K & 7) != 0 || (N & 7) != 0 || (epilogue != 0 && epilogue != 2) || M % BM != 0 || n_experts <= 0 ||
+        tile_expert == nullptr || (long long)n_experts * N > 0x7fffffffLL)
+        return RLIS_ERR_UNSUPPORTED;
+    if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
+        return RLIS_ERR_UNSUPPORTED;
+    CUtensorMap map_x, map_w;
+    if (!make_map(&map_x, x, M, K, BM) || !make_map(&map_w, W, n_experts * N, K, BN)) return RLIS_ERR_UNSUPPORTED;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(gemm_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM);
+        cudaFuncSetAttribute(gemm_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM);
+        attr_done = true;
+    }
+    const int m_tiles = M / BM, num_tiles = m_tiles * ((N + BN - 1) / BN);
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
+    const GluParams gp{1.0f, INFINITY, 0.0f};
+    if (epilogue == 0)
+        rlis_launch(gemm_tcgen05_kernel<0>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp,
+                    tile_expert, N);
+    else
+        rlis_launch(gemm_tcgen05_kernel<2>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp,
+                    tile_expert, N);
     return RLIS_LAUNCH_CHECK();
 }
 

@@ -168,7 +168,7 @@ template <typename T, bool GLU>
 __global__ __launch_bounds__(256) void moe_gemm_kernel(
     const T* __restrict__ A, const T* __restrict__ Wg, const T* __restrict__ Wu, void* __restrict__ out_,
     const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert, int top, int N, int K,
-    float slope, float limit, float shift, int tile_rows) {
+    float slope, float limit, float shift, int tile_rows, long long w_stride) {
     pdl_wait();
     const int e = tile_expert[blockIdx.y * BM / tile_rows];
     if (e < 0) return;
@@ -182,8 +182,8 @@ __global__ __launch_bounds__(256) void moe_gemm_kernel(
         rows[threadIdx.x] = pair < 0 ? -1 : (GLU ? pair / top : slot0 + (int)threadIdx.x);
     }
     __syncthreads();
-    const T* wg = Wg + (size_t)e * N * K;
-    const T* wu = GLU ? Wu + (size_t)e * N * K : nullptr;
+    const T* wg = Wg + (size_t)e * w_stride;
+    const T* wu = GLU ? Wu + (size_t)e * w_stride : nullptr;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     float accg[2][4], accu[2][4];
 #pragma unroll
@@ -317,21 +317,53 @@ extern "C" int rlis_moe_align(const int* top_idx, int* sorted_pair, int* pair_sl
     return RLIS_LAUNCH_CHECK();
 }
 
-// glu != 0: A [T, K] rows of tokens, Wg and Wu [n_experts, N, K], out [max_tiles * tile_rows, N] in the element type.
+// Rows of a step's tokens into slot order: out[slot, :] = x[token of the slot's pair, :], zeros in empty slots.
+template <typename T>
+__global__ __launch_bounds__(128) void moe_gather_rows_kernel(const T* __restrict__ x, T* __restrict__ out,
+                                                              const int* __restrict__ sorted_pair, int top, int width) {
+    pdl_wait_and_trigger();
+    const int pair = sorted_pair[blockIdx.x];
+    const T* src = pair >= 0 ? x + (size_t)(pair / top) * width : nullptr;
+    T* dst = out + (size_t)blockIdx.x * width;
+    constexpr int V = 16 / sizeof(T);
+    if (width % V == 0) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        for (int i = threadIdx.x; i < width / V; i += blockDim.x) d4[i] = src != nullptr ? s4[i] : make_uint4(0u, 0u, 0u, 0u);
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src != nullptr ? src[i] : from_f<T>(0.f);
+    }
+}
+
+// glu != 0: A [T, K] rows of tokens, Wg and Wu [n_experts, N, K] (experts w_stride elements apart), out
+// [max_tiles * tile_rows, N] in the element type.
 // glu == 0: A [max_tiles * tile, K] rows of slots, Wg [n_experts, N, K], out float32 [max_tiles * tile, N].
 extern "C" int rlis_moe_gemm(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair,
                              const int* tile_expert, int max_tiles, int tile_rows, int top, int N, int K, int glu,
-                             float slope, float limit, float shift, int dtype, cudaStream_t stream) {
+                             float slope, float limit, float shift, long long w_stride, int dtype, cudaStream_t stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
     if (tile_rows <= 0 || tile_rows % BM != 0) return RLIS_ERR_UNSUPPORTED;
     dim3 grid((N + BN - 1) / BN, max_tiles * (tile_rows / BM));
     if (grid.y > 65535) return RLIS_ERR_UNSUPPORTED;
 #define RLIS_MOE(T, G) rlis_launch(moe_gemm_kernel<T, G>, grid, 256, 0, stream, (const T*)A, (const T*)Wg, (const T*)Wu, \
-                                   out, sorted_pair, tile_expert, top, N, K, slope, limit, shift, tile_rows)
+                                   out, sorted_pair, tile_expert, top, N, K, slope, limit, shift, tile_rows, w_stride)
     if (dtype == RLIS_F32) { if (glu) RLIS_MOE(float, true); else RLIS_MOE(float, false); }
     else if (dtype == RLIS_BF16) { if (glu) RLIS_MOE(bf16, true); else RLIS_MOE(bf16, false); }
     else return RLIS_ERR_UNSUPPORTED;
 #undef RLIS_MOE
+    return RLIS_LAUNCH_CHECK();
+}
+
+// x [T, width] -> out [n_slots, width] in slot order (see moe_gather_rows_kernel).
+extern "C" int rlis_moe_gather_rows(const void* x, void* out, const int* sorted_pair, int n_slots, int top, int width,
+                                    int dtype, cudaStream_t stream) {
+    if (n_slots <= 0 || width <= 0) return 0;
+    if (dtype == RLIS_F32)
+        rlis_launch(moe_gather_rows_kernel<float>, n_slots, 128, 0, stream, (const float*)x, (float*)out, sorted_pair, top, width);
+    else if (dtype == RLIS_BF16)
+        rlis_launch(moe_gather_rows_kernel<bf16>, n_slots, 128, 0, stream, (const bf16*)x, (bf16*)out, sorted_pair, top, width);
+    else
+        return RLIS_ERR_UNSUPPORTED;
     return RLIS_LAUNCH_CHECK();
 }
 

@@ -21,7 +21,7 @@ template <bool GLU, int TM>
 __global__ __launch_bounds__(TM == 128 ? 256 : TM * 4) void moe_mma_kernel(
     const bf16* __restrict__ A, const bf16* __restrict__ Wg, const bf16* __restrict__ Wu, void* __restrict__ out_,
     const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert, int top, int N, int K,
-    float slope, float limit, float shift) {
+    float slope, float limit, float shift, long long w_stride) {
     constexpr int MT = TM == 128 ? 2 : 1;            // fragments of 16 slots a warp
     constexpr int THREADS = TM * 4 / MT;             // TM / (16 MT) x 2 warps
     constexpr int STAGE = MoeSmem<GLU, TM>::STAGE;
@@ -37,8 +37,8 @@ __global__ __launch_bounds__(TM == 128 ? 256 : TM * 4) void moe_mma_kernel(
         rows[threadIdx.x] = pair < 0 ? -1 : (GLU ? pair / top : slot0 + (int)threadIdx.x);
     }
     __syncthreads();
-    const bf16* wg = Wg + (size_t)e * N * K;
-    const bf16* wu = GLU ? Wu + (size_t)e * N * K : nullptr;
+    const bf16* wg = Wg + (size_t)e * w_stride;
+    const bf16* wu = GLU ? Wu + (size_t)e * w_stride : nullptr;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wm = warp >> 1, wn = warp & 1;         // a warp: 16 MT slots x 32 features
     const int g = lane >> 2, c = lane & 3;
@@ -147,7 +147,8 @@ __global__ __launch_bounds__(TM == 128 ? 256 : TM * 4) void moe_mma_kernel(
 
 template <bool GLU, int TM>
 int launch(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair, const int* tile_expert,
-           int max_tiles, int top, int N, int K, float slope, float limit, float shift, cudaStream_t stream) {
+           int max_tiles, int top, int N, int K, float slope, float limit, float shift, long long w_stride,
+           cudaStream_t stream) {
     constexpr size_t smem = (size_t)STAGES * MoeSmem<GLU, TM>::STAGE * sizeof(bf16);
     static bool raised = false;
     if (!raised) {
@@ -156,7 +157,7 @@ int launch(const void* A, const void* Wg, const void* Wu, void* out, const int* 
     }
     dim3 grid((N + TN - 1) / TN, max_tiles);
     rlis_launch(moe_mma_kernel<GLU, TM>, grid, TM == 128 ? 256 : TM * 4, smem, stream, (const bf16*)A, (const bf16*)Wg, (const bf16*)Wu, out,
-                sorted_pair, tile_expert, top, N, K, slope, limit, shift);
+                sorted_pair, tile_expert, top, N, K, slope, limit, shift, w_stride);
     return RLIS_LAUNCH_CHECK();
 }
 }  // namespace
@@ -165,10 +166,10 @@ int launch(const void* A, const void* Wg, const void* Wu, void* out, const int* 
 // tiles of 32 or 128 slots.
 extern "C" int rlis_moe_gemm_mma(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair,
                                  const int* tile_expert, int max_tiles, int tile_rows, int top, int N, int K, int glu,
-                                 float slope, float limit, float shift, cudaStream_t stream) {
+                                 float slope, float limit, float shift, long long w_stride, cudaStream_t stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
     if (K % 8 != 0 || K <= 0 || max_tiles > 65535 || (tile_rows != 32 && tile_rows != 128)) return RLIS_ERR_UNSUPPORTED;
-#define RLIS_MM(G, T) launch<G, T>(A, Wg, Wu, out, sorted_pair, tile_expert, max_tiles, top, N, K, slope, limit, shift, stream)
+#define RLIS_MM(G, T) launch<G, T>(A, Wg, Wu, out, sorted_pair, tile_expert, max_tiles, top, N, K, slope, limit, shift, w_stride, stream)
     if (tile_rows == 32) return glu ? RLIS_MM(true, 32) : RLIS_MM(false, 32);
     return glu ? RLIS_MM(true, 128) : RLIS_MM(false, 128);
 #undef RLIS_MM

@@ -877,7 +877,8 @@ def _set_stream_rows(value):
     STREAM_GEMM_ROWS = max(DECODE_GEMM_ROWS, min(int(value), STREAM_MAX_ROWS))
 
 
-library.PYTHON_SWITCHES.update(biased_mma=_set_flag("BIASED_MMA"), moe_mma=_set_flag("MOE_MMA"), fuse_norms=_set_flag("FUSE_NORMS"), prefill_tcgen05=_set_flag("PREFILL_TCGEN05"),
+library.PYTHON_SWITCHES.update(biased_mma=_set_flag("BIASED_MMA"), moe_mma=_set_flag("MOE_MMA"),
+                               moe_grouped=_set_flag("MOE_GROUPED"), fuse_norms=_set_flag("FUSE_NORMS"), prefill_tcgen05=_set_flag("PREFILL_TCGEN05"),
                                latent_mma=_set_flag("LATENT_MMA"), latent_ctas_per_sm=_set_latent_ctas,
                                stream_rows=_set_stream_rows)
 
@@ -1118,11 +1119,24 @@ def moe_tile_rows(n_pairs: int, n_experts: int) -> int:
     return 128 if n_pairs >= 96 * n_experts else 32
 
 
+MOE_GROUPED = True         # debug switch "moe_grouped": 0 keeps the experts' products over prompts on mma.sync
+
+
+def _expert_matrices(w, name: str, dtype, shape) -> int:
+    """Checks a stack of expert matrices [experts, N, K] whose experts may lie further apart than N * K
+    (a slice of a wider stack); returns the distance between experts in elements."""
+    if (not w.is_cuda or w.dtype != dtype or tuple(w.shape) != tuple(shape) or w.stride(2) != 1
+            or w.stride(1) != w.shape[2] or w.stride(0) < w.shape[1] * w.shape[2]):
+        raise KernelError(f"{name}: expected {dtype} expert matrices {tuple(shape)} with contiguous rows, got "
+                          f"{w.dtype} {tuple(w.shape)} with strides {w.stride()}")
+    return int(w.stride(0))
+
+
 def _moe_gemm(a, wg, wu, out, plan, N: int, K: int, glu: bool, slope: float, limit: float, shift: float, name: str):
     """One of the routed products: tensor cores for bfloat16 rows that are 16-byte multiples, FFMA otherwise."""
     args = (a.data_ptr(), wg.data_ptr(), wu.data_ptr() if wu is not None else None, out.data_ptr(),
             plan.sorted_pair.data_ptr(), plan.tile_expert.data_ptr(), plan.max_tiles, plan.tile, plan.top, N, K,
-            1 if glu else 0, float(slope), float(limit), float(shift))
+            1 if glu else 0, float(slope), float(limit), float(shift), int(wg.stride(0)))
     if MOE_MMA and a.dtype == torch.bfloat16 and K % 8 == 0 and lib().rlis_moe_mma_takes_tile(plan.tile):
         check(lib().rlis_moe_gemm_mma(*args, _stream()), name)
         _count("moe_gemm.mma" + (".glu" if glu else ".down"))
@@ -1163,16 +1177,52 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: in
                    shared_gate=gate if shared_gate else None)
 
 
+def _moe_grouped(plan: MoePlan, dtype, N: int, K: int) -> bool:
+    """Whether a routed product of this step goes to the grouped tcgen05 product: bfloat16, the sort's wide
+    tiles (its row tile), extents that its tensor maps take."""
+    return bool(MOE_GROUPED and dtype == torch.bfloat16 and plan.tile == 128 and K % 8 == 0 and N % 8 == 0 and N >= 256)
+
+
+def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[m] = x[m] @ w[e]^T for every row tile of 128 rows of x, e = tile_expert[tile] (-1: the tile is left
+    out and its rows of `out` keep what they held); on the tcgen05 tensor cores, one SM a tile.  x [M, K]
+    bfloat16 with M a multiple of 128; w [experts, N, K] bfloat16 contiguous; out [M, N] bfloat16 or float32."""
+    M, K = x.shape
+    E, N, _ = w.shape
+    _req(x, "x", torch.bfloat16)
+    _req(w, "w", torch.bfloat16, (E, N, K))
+    _req(tile_expert, "tile_expert", torch.int32, (None,))
+    _req(out, "out", None, (M, N))
+    if M % 128 or tile_expert.shape[0] < M // 128 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"gemm_tcgen05_grouped: rows in tiles of 128 with an expert each, got M={M} and "
+                          f"{tile_expert.shape[0]} tiles; out in bfloat16 or float32, got {out.dtype}")
+    check(lib().rlis_gemm_tcgen05_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, E, tile_expert.data_ptr(),
+                                          2 if out.dtype == torch.float32 else 0, _stream()), "gemm_tcgen05_grouped")
+    _count("gemm_tcgen05.grouped")
+    return out
+
+
 def moe_up(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, plan: MoePlan, slope: float, limit: float,
-           up_shift: float, step) -> torch.Tensor:
+           up_shift: float, step, w_gate_up: torch.Tensor | None = None) -> torch.Tensor:
     """act[slot, :] = glu(w_gate[e] x_t, w_up[e] x_t) for the token t and expert e of every slot (see `glu_act`);
-    w_gate, w_up [experts, I, width]; returns [slots, I] in x's type."""
+    w_gate, w_up [experts, I, width] (possibly the two halves of `w_gate_up` [experts, 2 I, width], which the
+    grouped tcgen05 product over prompts wants in one piece); returns [slots, I] in x's type."""
     T, W = x.shape
     E, I, _ = w_gate.shape
     _req(x, "x")
-    _req(w_gate, "w_gate", x.dtype, (plan.n_experts, I, W))
-    _req(w_up, "w_up", x.dtype, (plan.n_experts, I, W))
-    act = step.buffer("moe_act", (plan.max_tiles * plan.tile, I), x.dtype)
+    _expert_matrices(w_gate, "w_gate", x.dtype, (plan.n_experts, I, W))
+    if _expert_matrices(w_up, "w_up", x.dtype, (plan.n_experts, I, W)) != w_gate.stride(0):
+        raise KernelError("moe_up: gate and linear branch must lie equally far apart from expert to expert")
+    S = plan.max_tiles * plan.tile
+    act = step.buffer("moe_act", (S, I), x.dtype)
+    if w_gate_up is not None and _moe_grouped(plan, x.dtype, 2 * I, W):
+        # rows into slot order, one grouped product for both branches, then the gating
+        xs = step.buffer("moe_rows", (S, W), x.dtype)
+        check(lib().rlis_moe_gather_rows(x.data_ptr(), xs.data_ptr(), plan.sorted_pair.data_ptr(), S, plan.top, W,
+                                         _code(x.dtype), _stream()), "moe_gather_rows")
+        _count("moe_gather_rows")
+        gu = gemm_tcgen05_grouped(xs, w_gate_up, plan.tile_expert, step.buffer("moe_gate_up", (S, 2 * I), x.dtype))
+        return glu_act(gu, act, slope, None if limit == float("inf") else limit, up_shift)
     _moe_gemm(x, w_gate, w_up, act, plan, I, W, True, slope, limit, up_shift, "moe_up")
     return act
 
@@ -1182,8 +1232,10 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan, step) -> to
     S, I = act.shape
     E, W, _ = w_down.shape
     _req(act, "act", None, (plan.max_tiles * plan.tile, I))
-    _req(w_down, "w_down", act.dtype, (plan.n_experts, W, I))
+    _expert_matrices(w_down, "w_down", act.dtype, (plan.n_experts, W, I))
     y = step.buffer("moe_y", (S, W), torch.float32)
+    if w_down.is_contiguous() and _moe_grouped(plan, act.dtype, W, I):
+        return gemm_tcgen05_grouped(act, w_down, plan.tile_expert, y)
     _moe_gemm(act, w_down, None, y, plan, W, I, False, 1.0, 0.0, 0.0, "moe_down")
     return y
 

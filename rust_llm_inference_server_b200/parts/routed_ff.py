@@ -51,8 +51,12 @@ class RoutedFF(FeedForward):
             rows.append(src.get(s.shared_gate, "vector"))
         self.w_router = torch.cat(rows, dim=0).contiguous()              # float32 [experts (+ 1), hidden]
         self.correction = src.get(s.correction, "vector").contiguous() if s.correction is not None else None
-        self.w_gate = torch.stack([src.get(n) for n in self._names(s.gate_proj)]).contiguous()
-        self.w_up = torch.stack([src.get(n) for n in self._names(s.up_proj)]).contiguous()
+        # [expert, gate rows | linear rows, in]: one stack, so that the grouped product over prompts forms both
+        # branches at once; the two halves are views of it
+        self.w_gate_up = torch.stack([torch.cat([src.get(g), src.get(u)], dim=0)
+                                      for g, u in zip(self._names(s.gate_proj), self._names(s.up_proj))]).contiguous()
+        self.w_gate = self.w_gate_up[:, :s.intermediate]
+        self.w_up = self.w_gate_up[:, s.intermediate:]
         self.w_down = torch.stack([src.get(n) for n in self._names(s.down_proj)]).contiguous()
         if self.shared is not None:
             self.shared.load(src)
@@ -65,7 +69,7 @@ class RoutedFF(FeedForward):
                                  s.shared_gate is not None, step)
         y_shared = self.shared.forward(x, step) if self.shared is not None else None
         with span("experts"):
-            act = ops.moe_up(x, self.w_gate, self.w_up, plan, s.slope, self.limit, s.up_shift, step)
+            act = ops.moe_up(x, self.w_gate, self.w_up, plan, s.slope, self.limit, s.up_shift, step, self.w_gate_up)
             y = ops.moe_down(act, self.w_down, plan, step)
         out = step.buffer("ffn_out", (T, s.hidden), self.dtype)
         with span("combine"):

@@ -287,7 +287,8 @@ def test_attention_far_keys_table_rows_page_borders_and_gates(dtype, H, G, d, dv
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,E,top,W,I", [(1, 3, 1, 40, 24), (37, 5, 2, 96, 40), (150, 9, 3, 64, 72), (64, 4, 4, 32, 16),
-                                          (300, 3, 2, 64, 48)])         # the last: wide tiles of the sort
+                                          (300, 3, 2, 64, 48),          # wide tiles of the sort
+                                          (600, 3, 2, 256, 128)])       # ... and sizes the grouped tcgen05 product takes
 def test_routing_choice_sort_and_experts(dtype, T, E, top, W, I):
     from rust_llm_inference_server_b200 import ops
     rng = np.random.default_rng(T)
@@ -305,13 +306,17 @@ def test_routing_choice_sort_and_experts(dtype, T, E, top, W, I):
     # the sort: every pair sits in exactly one slot, of a tile of its expert
     sp, ps, te = plan.sorted_pair.cpu().numpy(), plan.pair_slot.cpu().numpy(), plan.tile_expert.cpu().numpy()
     assert sorted(sp[sp >= 0].tolist()) == list(range(T * top))
-    assert plan.tile == (128 if T == 300 else 32)
+    assert plan.tile == (128 if T >= 300 else 32)
     for pair in range(T * top):
         assert sp[ps[pair]] == pair and te[ps[pair] // plan.tile] == idx.reshape(-1)[pair]
-    wg, wu = (dev(rng.standard_normal((E, I, W)) / np.sqrt(W), dtype) for _ in range(2))
+    wgu = dev(rng.standard_normal((E, 2 * I, W)) / np.sqrt(W), dtype)      # gate rows, then the linear branch's
+    wg, wu = wgu[:, :I], wgu[:, I:]
     wd = dev(rng.standard_normal((E, W, I)) / np.sqrt(I), dtype)
-    act = ops.moe_up(x, wg, wu, plan, 1.702, 0.9, 1.0, st)
+    ops.launches_by_kernel.clear()
+    act = ops.moe_up(x, wg, wu, plan, 1.702, 0.9, 1.0, st, wgu)
     y = ops.moe_down(act, wd, plan, st)
+    grouped = dtype == torch.bfloat16 and T == 600
+    assert ops.launches_by_kernel.get("gemm_tcgen05.grouped", 0) == (2 if grouped else 0)
     shared = dev(rng.standard_normal((T, W)), dtype)
     out = torch.empty((T, W), dtype=dtype, device="cuda")
     ops.moe_combine(y, plan, shared, out)
@@ -321,6 +326,7 @@ def test_routing_choice_sort_and_experts(dtype, T, E, top, W, I):
             want[t] += wt * P.clipped_glu(host(x)[t:t + 1], host(wg)[e], host(wu)[e], host(wd)[e], 0.9)[0]
     want += P.sigmoid(host(x) @ host(wr)[E])[:, None] * host(shared)
     np.testing.assert_allclose(host(out), want, rtol=0, atol=3e-5 if dtype == torch.float32 else 0.06)
+    ops.check_device_errors()
     # without a shared expert and without a correction
     plan = ops.moe_route(x, wr[:E].contiguous(), None, E, top, 1.0, False, st)
     assert plan.shared_gate is None
