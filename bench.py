@@ -669,13 +669,12 @@ def gavodra_kernel_rooflines(width: int, B: int, ctx: int, T: int, pk: dict, tor
         # feed-forward products at the same number of feed-forward columns a token (top * ff)
         x = rnd(n, width).to(bf)
         wr, corr = rnd(E, width).contiguous(), rnd(E).contiguous()
-        wgu, wd = rnd(E, 2 * ff, width).to(bf), rnd(E, width, ff).to(bf)     # gate rows, then the linear branch's
-        wg, wu = wgu[:, :ff], wgu[:, ff:]
+        wgu, wd = rnd(E, 2 * ff, width).to(bf), rnd(E, width, ff).to(bf)     # gate and linear rows in blocks of 4
         y = torch.empty(n, width, dtype=bf, device="cuda")
 
         def routed():
             plan = ops.moe_route(x, wr, corr, E, top, 2.5, False, st)
-            act = ops.moe_up(x, wg, wu, plan, 1.702, 7.0, 1.0, st, wgu)
+            act = ops.moe_up(x, wgu, plan, 1.702, 7.0, 1.0, st, 4)
             return ops.moe_combine(ops.moe_down(act, wd, plan, st), plan, None, y)
         used = min(E, n * top)
         flops = 2.0 * n * top * 3 * ff * width

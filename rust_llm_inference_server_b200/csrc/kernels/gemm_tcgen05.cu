@@ -218,12 +218,15 @@ static int gemm_tcgen05_impl(const void* x, const void* W, void* y, int M, int N
 
 // Grouped form: x [M, K] in row tiles of 128 (M a multiple of 128), row tile m multiplied by expert
 // tile_expert[m]'s matrix W[e] [N, K] of W [n_experts, N, K] (-1: the tile is left out); epilogue 0 (bf16
-// y [M, N]) or 2 (float32).  One SM a tile.  tile_expert is read on the device: nothing of it reaches the host.
+// y [M, N]), 2 (float32) or 3 (W's rows interleaved gate/up in blocks of 4, y [M, N / 2] bf16 gated with slope,
+// limit and shift).  One SM a tile.  tile_expert is read on the device: nothing of it reaches the host.
 extern "C" int rlis_gemm_tcgen05_grouped(const void* x, const void* W, void* y, int M, int N, int K, int n_experts,
-                                         const int* tile_expert, int epilogue, cudaStream_t stream) {
+                                         const int* tile_expert, int epilogue, float slope, float limit, float shift,
+                                         cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || (K & 7) != 0 || (N & 7) != 0 || (epilogue != 0 && epilogue != 2) || M % BM != 0 || n_experts <= 0 ||
-        tile_expert == nullptr || (long long)n_experts * N > 0x7fffffffLL)
+    if (K <= 0 || (K & 7) != 0 || (N & 7) != 0 || (epilogue != 0 && epilogue != 2 && epilogue != 3) || M % BM != 0 ||
+        n_experts <= 0 || tile_expert == nullptr || (long long)n_experts * N > 0x7fffffffLL ||
+        (epilogue == 3 && (N & 15) != 0))
         return RLIS_ERR_UNSUPPORTED;
     if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
         return RLIS_ERR_UNSUPPORTED;
@@ -233,18 +236,22 @@ extern "C" int rlis_gemm_tcgen05_grouped(const void* x, const void* W, void* y, 
     if (!attr_done) {
         cudaFuncSetAttribute(gemm_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM);
         cudaFuncSetAttribute(gemm_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM);
+        cudaFuncSetAttribute(gemm_tcgen05_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GT_SMEM);
         attr_done = true;
     }
     const int m_tiles = M / BM, num_tiles = m_tiles * ((N + BN - 1) / BN);
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
-    const GluParams gp{1.0f, INFINITY, 0.0f};
+    const GluParams gp{slope, limit, shift};
     if (epilogue == 0)
         rlis_launch(gemm_tcgen05_kernel<0>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp,
                     tile_expert, N);
-    else
+    else if (epilogue == 2)
         rlis_launch(gemm_tcgen05_kernel<2>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp,
+                    tile_expert, N);
+    else
+        rlis_launch(gemm_tcgen05_kernel<3>, grid, GT_THREADS, GT_SMEM, stream, map_x, map_w, y, M, N, K, m_tiles, num_tiles, gp,
                     tile_expert, N);
     return RLIS_LAUNCH_CHECK();
 }

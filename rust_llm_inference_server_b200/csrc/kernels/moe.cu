@@ -168,7 +168,7 @@ template <typename T, bool GLU>
 __global__ __launch_bounds__(256) void moe_gemm_kernel(
     const T* __restrict__ A, const T* __restrict__ Wg, const T* __restrict__ Wu, void* __restrict__ out_,
     const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert, int top, int N, int K,
-    float slope, float limit, float shift, int tile_rows, long long w_stride) {
+    float slope, float limit, float shift, int tile_rows, long long w_stride, int il) {
     pdl_wait();
     const int e = tile_expert[blockIdx.y * BM / tile_rows];
     if (e < 0) return;
@@ -200,8 +200,10 @@ __global__ __launch_bounds__(256) void moe_gemm_kernel(
             const int r = i / BK, c = i % BK;
             const int gn = n0 + r, gk = k0 + c;
             const bool in = gn < N && gk < K;
-            Gs[c][r] = in ? to_f<T>(wg[(size_t)gn * K + gk]) : 0.f;
-            if (GLU) Us[c][r] = in ? to_f<T>(wu[(size_t)gn * K + gk]) : 0.f;
+            // (il > 0: blocks of il gate rows, each followed by its il rows of the linear branch; Wu starts il rows in)
+            const size_t wrow = il > 0 ? (size_t)(gn / il) * 2 * il + gn % il : (size_t)gn;
+            Gs[c][r] = in ? to_f<T>(wg[wrow * K + gk]) : 0.f;
+            if (GLU) Us[c][r] = in ? to_f<T>(wu[wrow * K + gk]) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -336,17 +338,21 @@ __global__ __launch_bounds__(128) void moe_gather_rows_kernel(const T* __restric
 }
 
 // glu != 0: A [T, K] rows of tokens, Wg and Wu [n_experts, N, K] (experts w_stride elements apart), out
-// [max_tiles * tile_rows, N] in the element type.
+// [max_tiles * tile_rows, N] in the element type.  interleave B > 0: gate and linear branch share one stack
+// [n_experts, 2 N, K] in blocks of B gate rows, each followed by its B rows of the linear branch; Wg points
+// at its first row and Wu B rows further.
 // glu == 0: A [max_tiles * tile, K] rows of slots, Wg [n_experts, N, K], out float32 [max_tiles * tile, N].
 extern "C" int rlis_moe_gemm(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair,
                              const int* tile_expert, int max_tiles, int tile_rows, int top, int N, int K, int glu,
-                             float slope, float limit, float shift, long long w_stride, int dtype, cudaStream_t stream) {
+                             float slope, float limit, float shift, long long w_stride, int interleave, int dtype,
+                             cudaStream_t stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
-    if (tile_rows <= 0 || tile_rows % BM != 0) return RLIS_ERR_UNSUPPORTED;
+    if (tile_rows <= 0 || tile_rows % BM != 0 || interleave < 0 || (interleave > 0 && N % interleave != 0))
+        return RLIS_ERR_UNSUPPORTED;
     dim3 grid((N + BN - 1) / BN, max_tiles * (tile_rows / BM));
     if (grid.y > 65535) return RLIS_ERR_UNSUPPORTED;
 #define RLIS_MOE(T, G) rlis_launch(moe_gemm_kernel<T, G>, grid, 256, 0, stream, (const T*)A, (const T*)Wg, (const T*)Wu, \
-                                   out, sorted_pair, tile_expert, top, N, K, slope, limit, shift, tile_rows, w_stride)
+                                   out, sorted_pair, tile_expert, top, N, K, slope, limit, shift, tile_rows, w_stride, interleave)
     if (dtype == RLIS_F32) { if (glu) RLIS_MOE(float, true); else RLIS_MOE(float, false); }
     else if (dtype == RLIS_BF16) { if (glu) RLIS_MOE(bf16, true); else RLIS_MOE(bf16, false); }
     else return RLIS_ERR_UNSUPPORTED;

@@ -21,7 +21,7 @@ template <bool GLU, int TM>
 __global__ __launch_bounds__(TM == 128 ? 256 : TM * 4) void moe_mma_kernel(
     const bf16* __restrict__ A, const bf16* __restrict__ Wg, const bf16* __restrict__ Wu, void* __restrict__ out_,
     const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert, int top, int N, int K,
-    float slope, float limit, float shift, long long w_stride) {
+    float slope, float limit, float shift, long long w_stride, int il) {
     constexpr int MT = TM == 128 ? 2 : 1;            // fragments of 16 slots a warp
     constexpr int THREADS = TM * 4 / MT;             // TM / (16 MT) x 2 warps
     constexpr int STAGE = MoeSmem<GLU, TM>::STAGE;
@@ -64,7 +64,9 @@ __global__ __launch_bounds__(TM == 128 ? 256 : TM * 4) void moe_mma_kernel(
             const int r = rem >> 3, ch = rem & 7;
             const int gn = n0 + r, gk = k0 + ch * 8;
             const bool ok = gn < N && gk < K;
-            const size_t off = ok ? (size_t)gn * K + gk : 0;
+            // (il 4: blocks of 4 gate rows, each followed by its 4 rows of the linear branch; wu starts 4 rows in)
+            const size_t wrow = il == 4 ? (size_t)(((gn >> 2) << 3) + (gn & 3)) : (size_t)gn;
+            const size_t off = ok ? wrow * K + gk : 0;
             cp_async16((which ? us : gs) + r * SA + ch * 8, (which ? wu : wg) + off, ok);
         }
         cp_async_commit();
@@ -147,7 +149,7 @@ __global__ __launch_bounds__(TM == 128 ? 256 : TM * 4) void moe_mma_kernel(
 
 template <bool GLU, int TM>
 int launch(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair, const int* tile_expert,
-           int max_tiles, int top, int N, int K, float slope, float limit, float shift, long long w_stride,
+           int max_tiles, int top, int N, int K, float slope, float limit, float shift, long long w_stride, int il,
            cudaStream_t stream) {
     constexpr size_t smem = (size_t)STAGES * MoeSmem<GLU, TM>::STAGE * sizeof(bf16);
     static bool raised = false;
@@ -157,7 +159,7 @@ int launch(const void* A, const void* Wg, const void* Wu, void* out, const int* 
     }
     dim3 grid((N + TN - 1) / TN, max_tiles);
     rlis_launch(moe_mma_kernel<GLU, TM>, grid, TM == 128 ? 256 : TM * 4, smem, stream, (const bf16*)A, (const bf16*)Wg, (const bf16*)Wu, out,
-                sorted_pair, tile_expert, top, N, K, slope, limit, shift, w_stride);
+                sorted_pair, tile_expert, top, N, K, slope, limit, shift, w_stride, il);
     return RLIS_LAUNCH_CHECK();
 }
 }  // namespace
@@ -166,10 +168,13 @@ int launch(const void* A, const void* Wg, const void* Wu, void* out, const int* 
 // tiles of 32 or 128 slots.
 extern "C" int rlis_moe_gemm_mma(const void* A, const void* Wg, const void* Wu, void* out, const int* sorted_pair,
                                  const int* tile_expert, int max_tiles, int tile_rows, int top, int N, int K, int glu,
-                                 float slope, float limit, float shift, long long w_stride, cudaStream_t stream) {
+                                 float slope, float limit, float shift, long long w_stride, int interleave,
+                                 cudaStream_t stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
-    if (K % 8 != 0 || K <= 0 || max_tiles > 65535 || (tile_rows != 32 && tile_rows != 128)) return RLIS_ERR_UNSUPPORTED;
-#define RLIS_MM(G, T) launch<G, T>(A, Wg, Wu, out, sorted_pair, tile_expert, max_tiles, top, N, K, slope, limit, shift, w_stride, stream)
+    if (K % 8 != 0 || K <= 0 || max_tiles > 65535 || (tile_rows != 32 && tile_rows != 128) ||
+        (interleave != 0 && interleave != 4) || (interleave == 4 && N % 4 != 0))
+        return RLIS_ERR_UNSUPPORTED;
+#define RLIS_MM(G, T) launch<G, T>(A, Wg, Wu, out, sorted_pair, tile_expert, max_tiles, top, N, K, slope, limit, shift, w_stride, interleave, stream)
     if (tile_rows == 32) return glu ? RLIS_MM(true, 32) : RLIS_MM(false, 32);
     return glu ? RLIS_MM(true, 128) : RLIS_MM(false, 128);
 #undef RLIS_MM

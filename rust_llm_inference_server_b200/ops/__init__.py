@@ -1122,22 +1122,14 @@ def moe_tile_rows(n_pairs: int, n_experts: int) -> int:
 MOE_GROUPED = True         # debug switch "moe_grouped": 0 keeps the experts' products over prompts on mma.sync
 
 
-def _expert_matrices(w, name: str, dtype, shape) -> int:
-    """Checks a stack of expert matrices [experts, N, K] whose experts may lie further apart than N * K
-    (a slice of a wider stack); returns the distance between experts in elements."""
-    if (not w.is_cuda or w.dtype != dtype or tuple(w.shape) != tuple(shape) or w.stride(2) != 1
-            or w.stride(1) != w.shape[2] or w.stride(0) < w.shape[1] * w.shape[2]):
-        raise KernelError(f"{name}: expected {dtype} expert matrices {tuple(shape)} with contiguous rows, got "
-                          f"{w.dtype} {tuple(w.shape)} with strides {w.stride()}")
-    return int(w.stride(0))
-
-
-def _moe_gemm(a, wg, wu, out, plan, N: int, K: int, glu: bool, slope: float, limit: float, shift: float, name: str):
+def _moe_gemm(a, wg_ptr: int, wu_ptr, w_stride: int, interleave: int, out, plan, N: int, K: int, glu: bool,
+              slope: float, limit: float, shift: float, name: str):
     """One of the routed products: tensor cores for bfloat16 rows that are 16-byte multiples, FFMA otherwise."""
-    args = (a.data_ptr(), wg.data_ptr(), wu.data_ptr() if wu is not None else None, out.data_ptr(),
-            plan.sorted_pair.data_ptr(), plan.tile_expert.data_ptr(), plan.max_tiles, plan.tile, plan.top, N, K,
-            1 if glu else 0, float(slope), float(limit), float(shift), int(wg.stride(0)))
-    if MOE_MMA and a.dtype == torch.bfloat16 and K % 8 == 0 and lib().rlis_moe_mma_takes_tile(plan.tile):
+    args = (a.data_ptr(), wg_ptr, wu_ptr, out.data_ptr(), plan.sorted_pair.data_ptr(), plan.tile_expert.data_ptr(),
+            plan.max_tiles, plan.tile, plan.top, N, K, 1 if glu else 0, float(slope), float(limit), float(shift),
+            int(w_stride), int(interleave))
+    if (MOE_MMA and a.dtype == torch.bfloat16 and K % 8 == 0 and interleave in (0, 4)
+            and lib().rlis_moe_mma_takes_tile(plan.tile)):
         check(lib().rlis_moe_gemm_mma(*args, _stream()), name)
         _count("moe_gemm.mma" + (".glu" if glu else ".down"))
     else:
@@ -1183,47 +1175,62 @@ def _moe_grouped(plan: MoePlan, dtype, N: int, K: int) -> bool:
     return bool(MOE_GROUPED and dtype == torch.bfloat16 and plan.tile == 128 and K % 8 == 0 and N % 8 == 0 and N >= 256)
 
 
-def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor,
+                         glu: tuple | None = None) -> torch.Tensor:
     """out[m] = x[m] @ w[e]^T for every row tile of 128 rows of x, e = tile_expert[tile] (-1: the tile is left
     out and its rows of `out` keep what they held); on the tcgen05 tensor cores, one SM a tile.  x [M, K]
-    bfloat16 with M a multiple of 128; w [experts, N, K] bfloat16 contiguous; out [M, N] bfloat16 or float32."""
+    bfloat16 with M a multiple of 128; w [experts, N, K] bfloat16 contiguous; out [M, N] bfloat16 or float32.
+    With `glu` = (slope, limit or None, up_shift): w's rows are gate and linear branch interleaved in blocks of
+    4 and out [M, N / 2] bfloat16 is the gated result (see `glu_act`)."""
     M, K = x.shape
     E, N, _ = w.shape
     _req(x, "x", torch.bfloat16)
     _req(w, "w", torch.bfloat16, (E, N, K))
     _req(tile_expert, "tile_expert", torch.int32, (None,))
-    _req(out, "out", None, (M, N))
+    _req(out, "out", torch.bfloat16 if glu is not None else None, (M, N // 2 if glu is not None else N))
     if M % 128 or tile_expert.shape[0] < M // 128 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"gemm_tcgen05_grouped: rows in tiles of 128 with an expert each, got M={M} and "
                           f"{tile_expert.shape[0]} tiles; out in bfloat16 or float32, got {out.dtype}")
+    slope, limit, shift = glu if glu is not None else (1.0, None, 0.0)
+    code = 3 if glu is not None else 2 if out.dtype == torch.float32 else 0
     check(lib().rlis_gemm_tcgen05_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, E, tile_expert.data_ptr(),
-                                          2 if out.dtype == torch.float32 else 0, _stream()), "gemm_tcgen05_grouped")
-    _count("gemm_tcgen05.grouped")
+                                          code, float(slope), float("inf") if limit is None else float(limit),
+                                          float(shift), _stream()), "gemm_tcgen05_grouped")
+    _count("gemm_tcgen05.grouped" + (".glu4" if glu is not None else ""))
     return out
 
 
-def moe_up(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, plan: MoePlan, slope: float, limit: float,
-           up_shift: float, step, w_gate_up: torch.Tensor | None = None) -> torch.Tensor:
-    """act[slot, :] = glu(w_gate[e] x_t, w_up[e] x_t) for the token t and expert e of every slot (see `glu_act`);
-    w_gate, w_up [experts, I, width] (possibly the two halves of `w_gate_up` [experts, 2 I, width], which the
-    grouped tcgen05 product over prompts wants in one piece); returns [slots, I] in x's type."""
+def moe_up(x: torch.Tensor, w_gate_up: torch.Tensor, plan: MoePlan, slope: float, limit: float, up_shift: float,
+           step, interleave: int = 0) -> torch.Tensor:
+    """act[slot, :] = glu(w_gate[e] x_t, w_up[e] x_t) for the token t and expert e of every slot (see `glu_act`).
+    w_gate_up [experts, 2 I, width] holds both branches of every expert: interleave 0: the I gate rows, then the
+    I rows of the linear branch; interleave B > 0: blocks of B gate rows, each followed by its B rows of the
+    linear branch (4 is what the gated epilogue of the grouped tcgen05 product over prompts wants).  Returns
+    [slots, I] in x's type."""
     T, W = x.shape
-    E, I, _ = w_gate.shape
+    E, I2, _ = w_gate_up.shape
+    I = I2 // 2
     _req(x, "x")
-    _expert_matrices(w_gate, "w_gate", x.dtype, (plan.n_experts, I, W))
-    if _expert_matrices(w_up, "w_up", x.dtype, (plan.n_experts, I, W)) != w_gate.stride(0):
-        raise KernelError("moe_up: gate and linear branch must lie equally far apart from expert to expert")
+    _req(w_gate_up, "w_gate_up", x.dtype, (plan.n_experts, 2 * I, W))
+    if interleave < 0 or (interleave > 0 and I % interleave):
+        raise KernelError(f"moe_up: blocks of {interleave} rows do not divide {I}")
     S = plan.max_tiles * plan.tile
     act = step.buffer("moe_act", (S, I), x.dtype)
-    if w_gate_up is not None and _moe_grouped(plan, x.dtype, 2 * I, W):
-        # rows into slot order, one grouped product for both branches, then the gating
+    limit_or_none = None if limit == float("inf") else limit
+    if interleave in (0, 4) and _moe_grouped(plan, x.dtype, 2 * I, W) and (interleave == 0 or I % 8 == 0):
+        # rows into slot order, then one grouped product for both branches; in blocks of 4 it gates on its
+        # accumulators, otherwise the gating is a pass of its own
         xs = step.buffer("moe_rows", (S, W), x.dtype)
         check(lib().rlis_moe_gather_rows(x.data_ptr(), xs.data_ptr(), plan.sorted_pair.data_ptr(), S, plan.top, W,
                                          _code(x.dtype), _stream()), "moe_gather_rows")
         _count("moe_gather_rows")
+        if interleave == 4:
+            return gemm_tcgen05_grouped(xs, w_gate_up, plan.tile_expert, act, glu=(slope, limit_or_none, up_shift))
         gu = gemm_tcgen05_grouped(xs, w_gate_up, plan.tile_expert, step.buffer("moe_gate_up", (S, 2 * I), x.dtype))
-        return glu_act(gu, act, slope, None if limit == float("inf") else limit, up_shift)
-    _moe_gemm(x, w_gate, w_up, act, plan, I, W, True, slope, limit, up_shift, "moe_up")
+        return glu_act(gu, act, slope, limit_or_none, up_shift)
+    rows_to_up = (interleave if interleave > 0 else I) * W * w_gate_up.element_size()
+    _moe_gemm(x, w_gate_up.data_ptr(), w_gate_up.data_ptr() + rows_to_up, 2 * I * W, interleave, act, plan, I, W, True,
+              slope, limit, up_shift, "moe_up")
     return act
 
 
@@ -1232,11 +1239,11 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, plan: MoePlan, step) -> to
     S, I = act.shape
     E, W, _ = w_down.shape
     _req(act, "act", None, (plan.max_tiles * plan.tile, I))
-    _expert_matrices(w_down, "w_down", act.dtype, (plan.n_experts, W, I))
+    _req(w_down, "w_down", act.dtype, (plan.n_experts, W, I))
     y = step.buffer("moe_y", (S, W), torch.float32)
-    if w_down.is_contiguous() and _moe_grouped(plan, act.dtype, W, I):
+    if _moe_grouped(plan, act.dtype, W, I):
         return gemm_tcgen05_grouped(act, w_down, plan.tile_expert, y)
-    _moe_gemm(act, w_down, None, y, plan, W, I, False, 1.0, 0.0, 0.0, "moe_down")
+    _moe_gemm(act, w_down.data_ptr(), None, W * I, 0, y, plan, W, I, False, 1.0, 0.0, 0.0, "moe_down")
     return y
 
 

@@ -46,10 +46,10 @@ SIGNATURES = {
     "rlis_attention_bias_decode": [P, P, P, P, P, P, I, P, LL, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
     "rlis_moe_route": [P, P, P, P, P, P, I, I, I, I, F, I, P],
     "rlis_moe_align": [P, P, P, P, I, I, I, I, P],
-    "rlis_moe_gemm": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, LL, I, P],
+    "rlis_moe_gemm": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, LL, I, I, P],
     "rlis_moe_gather_rows": [P, P, P, I, I, I, I, P],
-    "rlis_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, P, I, P],
-    "rlis_moe_gemm_mma": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, LL, P],
+    "rlis_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, P, I, F, F, F, P],
+    "rlis_moe_gemm_mma": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, LL, I, P],
     "rlis_moe_mma_takes_tile": [I],
     "rlis_moe_combine": [P, P, P, P, P, P, I, I, I, I, P],
     "rlis_glu_act": [P, P, I, I, F, F, F, I, I, P],

@@ -51,12 +51,18 @@ class RoutedFF(FeedForward):
             rows.append(src.get(s.shared_gate, "vector"))
         self.w_router = torch.cat(rows, dim=0).contiguous()              # float32 [experts (+ 1), hidden]
         self.correction = src.get(s.correction, "vector").contiguous() if s.correction is not None else None
-        # [expert, gate rows | linear rows, in]: one stack, so that the grouped product over prompts forms both
-        # branches at once; the two halves are views of it
-        self.w_gate_up = torch.stack([torch.cat([src.get(g), src.get(u)], dim=0)
-                                      for g, u in zip(self._names(s.gate_proj), self._names(s.up_proj))]).contiguous()
-        self.w_gate = self.w_gate_up[:, :s.intermediate]
-        self.w_up = self.w_gate_up[:, s.intermediate:]
+        # one stack [expert, 2 I, in] of both branches: gate and linear rows interleaved in blocks of 4 (what
+        # the gated epilogue of the grouped product over prompts wants) where I allows, else gate rows first
+        I, W = s.intermediate, s.hidden
+        self.interleave = 4 if I % 4 == 0 else 0
+        per_expert = []
+        for gn, un in zip(self._names(s.gate_proj), self._names(s.up_proj)):
+            g, u = src.get(gn), src.get(un)
+            if self.interleave:
+                per_expert.append(torch.stack([g.view(-1, 4, W), u.view(-1, 4, W)], dim=1).reshape(2 * I, W))
+            else:
+                per_expert.append(torch.cat([g, u], dim=0))
+        self.w_gate_up = torch.stack(per_expert).contiguous()
         self.w_down = torch.stack([src.get(n) for n in self._names(s.down_proj)]).contiguous()
         if self.shared is not None:
             self.shared.load(src)
@@ -69,7 +75,7 @@ class RoutedFF(FeedForward):
                                  s.shared_gate is not None, step)
         y_shared = self.shared.forward(x, step) if self.shared is not None else None
         with span("experts"):
-            act = ops.moe_up(x, self.w_gate, self.w_up, plan, s.slope, self.limit, s.up_shift, step, self.w_gate_up)
+            act = ops.moe_up(x, self.w_gate_up, plan, s.slope, self.limit, s.up_shift, step, self.interleave)
             y = ops.moe_down(act, self.w_down, plan, step)
         out = step.buffer("ffn_out", (T, s.hidden), self.dtype)
         with span("combine"):

@@ -309,13 +309,19 @@ def test_routing_choice_sort_and_experts(dtype, T, E, top, W, I):
     assert plan.tile == (128 if T >= 300 else 32)
     for pair in range(T * top):
         assert sp[ps[pair]] == pair and te[ps[pair] // plan.tile] == idx.reshape(-1)[pair]
-    wgu = dev(rng.standard_normal((E, 2 * I, W)) / np.sqrt(W), dtype)      # gate rows, then the linear branch's
-    wg, wu = wgu[:, :I], wgu[:, I:]
+    wg, wu = (dev(rng.standard_normal((E, I, W)) / np.sqrt(W), dtype) for _ in range(2))
     wd = dev(rng.standard_normal((E, W, I)) / np.sqrt(I), dtype)
+    # both branches in one stack: in blocks of 4 rows, and gate rows first
+    stacks = {4: torch.stack([wg.view(E, -1, 4, W), wu.view(E, -1, 4, W)], dim=2).reshape(E, 2 * I, W).contiguous(),
+              0: torch.cat([wg, wu], dim=1).contiguous()}
     ops.launches_by_kernel.clear()
-    act = ops.moe_up(x, wg, wu, plan, 1.702, 0.9, 1.0, st, wgu)
+    acts = {il: ops.moe_up(x, stack, plan, 1.702, 0.9, 1.0, st, il).clone() for il, stack in stacks.items()}
+    real = plan.sorted_pair >= 0
+    assert float((acts[4][real].float() - acts[0][real].float()).abs().max()) <= (0.0 if dtype == torch.float32 else 0.05)
+    act = acts[4]
     y = ops.moe_down(act, wd, plan, st)
     grouped = dtype == torch.bfloat16 and T == 600
+    assert ops.launches_by_kernel.get("gemm_tcgen05.grouped.glu4", 0) == (1 if grouped else 0)
     assert ops.launches_by_kernel.get("gemm_tcgen05.grouped", 0) == (2 if grouped else 0)
     shared = dev(rng.standard_normal((T, W)), dtype)
     out = torch.empty((T, W), dtype=dtype, device="cuda")
