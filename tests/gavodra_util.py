@@ -46,7 +46,7 @@ def model(vocab, width, eps, layers, residual_mult=None, emb_scale=None, logit_s
 
 
 # rows of the distance-bias tables of each configuration's layers (the checkpoint's shapes say it, not the file)
-BIAS_ROWS = {"A": [12, 12, 20, 12], "B": [9, 6, 9], "C": [16, 16, 10], "D": [7, 11]}
+BIAS_ROWS = {"A": [12, 12, 20, 12], "B": [9, 6, 9], "C": [16, 16, 10], "D": [7, 11], "E": [8, 14]}
 CONFIGS = {
     # a layer that does not mix before the first that does, a layer without feed-forward, dense and routed
     # feed-forwards in both orders, with and without a shared expert, limits that differ
@@ -75,7 +75,12 @@ CONFIGS["D"] = model(131, 100, 1e-5, [
     layer(attn(5, 5, 24, 20, 0.2, 19.0), moe(7, 3, 36, 1.4, 0.9, shared=(50, 1.1))),
     layer(attn(10, 5, 12, 20, 0.3, 45.0), dense(50, 2.2)),
 ], residual_mult=0.8, emb_scale=1.5, softcap=12.0)
-SEEDS = {"A": 3, "B": 5, "C": 8, "D": 13}
+# experts whose products over prompts go to the grouped tcgen05 product (wide tiles of the sort, 256 columns)
+CONFIGS["E"] = model(89, 256, 1e-5, [
+    layer(attn(4, 2, 64, 64, 0.12, 60.0), moe(4, 2, 128, 1.3, 1.2)),
+    layer(attn(2, 2, 128, 64, 0.08, 24.0), moe(3, 1, 256, 0.9, 2.0, shared=(128, 1.5))),
+], residual_mult=0.6, emb_scale=2.0, logit_scale=0.7)
+SEEDS = {"A": 3, "B": 5, "C": 8, "D": 13, "E": 21}
 
 
 def tensor_shapes(cfg: dict, bias_rows) -> dict:
