@@ -83,6 +83,76 @@ __global__ __launch_bounds__(WARPS * 32) void qk_norm_store_kernel(
     }
 }
 
+// The same with 16-byte loads and stores: d / VN lanes a (token, head) (VN elements a vector: 8 of bfloat16, 4
+// of float32), so a warp takes 32 VN / d of them; for head sizes d = VN * 2^k up to 32 VN, value widths that
+// are multiples of VN, and rows, offsets and pointers on 16-byte boundaries.
+template <typename T>
+__global__ __launch_bounds__(WARPS * 32) void qk_norm_store_vec_kernel(
+    const T* __restrict__ proj, long long stride, int q_off, int k_off, int v_off,
+    const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+    const T* __restrict__ v_other, long long v_other_stride, float lambda,
+    T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ slots,
+    int n_units, int nh, int nkv, int d, int dv, int page_size, int lanes) {
+    pdl_wait_and_trigger();
+    constexpr int VN = Vec16<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int sub = lane / lanes, li = lane - sub * lanes;          // which of the warp's units, and the lane in it
+    const int per_warp = 32 / lanes;
+    const int unit = (blockIdx.x * WARPS + (threadIdx.x >> 5)) * per_warp + sub;
+    const bool live = unit < n_units;
+    const int per = nh + nkv;
+    const int t = live ? unit / per : 0, u = live ? unit - t * per : 0;
+    const T* row = proj + (size_t)t * stride;
+    const bool is_q = u < nh;
+    const T* x = row + (is_q ? q_off + u * d : k_off + (u - nh) * d);
+    const float* w = is_q ? q_w : k_w;
+    float v[VN];
+    load16<T>(x + li * VN, v);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VN; ++i) ss = fmaf(v[i], v[i], ss);
+    for (int o = lanes >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // within the unit's lanes
+    if (!live) return;
+    const float r = w != nullptr ? 1.0f / sqrtf(ss / (float)d + eps) : 1.0f;
+    T* dst = nullptr;
+    long long vrow = -1;
+    if (is_q) {
+        dst = q_out + ((size_t)t * nh + u) * d;
+    } else {
+        const int slot = slots != nullptr ? slots[t] : -1;
+        if (slot >= 0) {
+            const long long r0 = ((long long)(slot / page_size) * nkv + (u - nh)) * page_size + slot % page_size;
+            dst = k_cache + r0 * d;
+            vrow = r0 * dv;
+        }
+    }
+    if (dst != nullptr) {
+        alignas(16) T o[VN];
+#pragma unroll
+        for (int i = 0; i < VN; ++i) o[i] = from_f<T>(w != nullptr ? v[i] * r * w[li * VN + i] : v[i]);
+        *reinterpret_cast<uint4*>(dst + li * VN) = *reinterpret_cast<const uint4*>(o);
+    }
+    if (vrow >= 0) {
+        const int g = u - nh;
+        const T* vs = row + v_off + g * dv;
+        const T* vo = v_other != nullptr ? v_other + (size_t)t * v_other_stride + g * dv : nullptr;
+        for (int c = li * VN; c < dv; c += lanes * VN) {
+            float a[VN];
+            load16<T>(vs + c, a);
+            if (vo != nullptr) {
+                float b[VN];
+                load16<T>(vo + c, b);
+#pragma unroll
+                for (int i = 0; i < VN; ++i) a[i] = (1.0f - lambda) * a[i] + lambda * b[i];
+            }
+            alignas(16) T o[VN];
+#pragma unroll
+            for (int i = 0; i < VN; ++i) o[i] = from_f<T>(a[i]);
+            *reinterpret_cast<uint4*>(v_cache + vrow + c) = *reinterpret_cast<const uint4*>(o);
+        }
+    }
+}
+
 template <typename T>
 __global__ __launch_bounds__(WARPS * 32) void attn_bias_kernel(
     const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
@@ -178,6 +248,30 @@ extern "C" int rlis_qk_norm_store(const void* proj, long long stride, int q_off,
     if (d <= 0 || d > MAX_D || dv <= 0 || nh <= 0 || nkv <= 0) return RLIS_ERR_UNSUPPORTED;
     const long long units = (long long)n_tokens * (nh + nkv);
     if (units > 0x7fffffffLL) return RLIS_ERR_UNSUPPORTED;
+    {
+        // the vector form where everything lies on 16-byte boundaries and a head is VN * 2^k elements
+        const int vn = dtype == RLIS_F32 ? 4 : 8;
+        const int lanes = d / vn;
+        const uintptr_t ptrs = reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(v_other) |
+                               reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) |
+                               reinterpret_cast<uintptr_t>(v_cache);
+        const bool vec = (dtype == RLIS_F32 || dtype == RLIS_BF16) && d % vn == 0 && dv % vn == 0 && lanes >= 1 &&
+                         lanes <= 32 && (lanes & (lanes - 1)) == 0 && (ptrs & 15) == 0 && stride % vn == 0 &&
+                         v_other_stride % vn == 0 && q_off % vn == 0 && k_off % vn == 0 && v_off % vn == 0;
+        if (vec) {
+            const int per_warp = 32 / lanes;
+            const unsigned vblocks = (unsigned)((units + (long long)WARPS * per_warp - 1) / (WARPS * per_warp));
+            if (dtype == RLIS_F32)
+                rlis_launch(qk_norm_store_vec_kernel<float>, vblocks, WARPS * 32, 0, stream, (const float*)proj, stride, q_off,
+                            k_off, v_off, q_w, k_w, eps, (const float*)v_other, v_other_stride, lambda, (float*)q_out,
+                            (float*)k_cache, (float*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, lanes);
+            else
+                rlis_launch(qk_norm_store_vec_kernel<bf16>, vblocks, WARPS * 32, 0, stream, (const bf16*)proj, stride, q_off,
+                            k_off, v_off, q_w, k_w, eps, (const bf16*)v_other, v_other_stride, lambda, (bf16*)q_out,
+                            (bf16*)k_cache, (bf16*)v_cache, slots, (int)units, nh, nkv, d, dv, page_size, lanes);
+            return RLIS_LAUNCH_CHECK();
+        }
+    }
     const unsigned blocks = (unsigned)((units + WARPS - 1) / WARPS);
     if (dtype == RLIS_F32)
         rlis_launch(qk_norm_store_kernel<float>, blocks, WARPS * 32, 0, stream, (const float*)proj, stride, q_off, k_off,
