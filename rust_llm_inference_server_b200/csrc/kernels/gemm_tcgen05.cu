@@ -53,6 +53,8 @@ constexpr uint32_t IDESC = idesc_bf16(BM, BN);
 // overlaps the products of the next one.
 // Grouped form (tile_expert given): row tile m of x belongs to expert tile_expert[m] (or to none: -1, the
 // tile is left out by every warp alike), whose N rows of W start at row expert * expert_rows of the map.
+// tile_expert[m_tiles] holds how many row tiles have an expert (they come first): the CTAs share out those
+// only, so that none of them draws mostly empty ones.
 template <int EPI>
 __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                   const __grid_constant__ CUtensorMap map_w,
@@ -68,6 +70,13 @@ __global__ __launch_bounds__(GT_THREADS) void gemm_tcgen05_kernel(const __grid_c
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (K + BK - 1) / BK;
+    if (tile_expert != nullptr) {
+        // (read by every thread from the same word, after the wait above: all roles agree)
+        const int n_tiles = num_tiles / m_tiles;
+        const int live = min(max(tile_expert[m_tiles], 0), m_tiles);
+        m_tiles = live > 0 ? live : 1;
+        num_tiles = live * n_tiles;
+    }
 
     if (threadIdx.x == 0) {
         ctrl->abort = 0;

@@ -125,7 +125,8 @@ __global__ __launch_bounds__(1024) void moe_route_kernel(
 }
 
 // One CTA.  pairs = tokens * top.  sorted_pair [max_tiles * tile]: the pair in a slot or -1; pair_slot [pairs];
-// tile_expert [max_tiles]: the expert of a tile of `tile` slots or -1 (no such tile).
+// tile_expert [max_tiles + 1]: the expert of a tile of `tile` slots or -1 (no such tile: they are the last
+// ones), and after them the number of tiles that have one.
 __global__ __launch_bounds__(1024) void moe_align_kernel(
     const int* __restrict__ top_idx, int* __restrict__ sorted_pair, int* __restrict__ pair_slot,
     int* __restrict__ tile_expert, int n_pairs, int n_experts, int max_tiles, int tile_rows) {
@@ -149,6 +150,7 @@ __global__ __launch_bounds__(1024) void moe_align_kernel(
             for (int i = 0; i < tiles && tile < max_tiles; ++i) tile_expert[tile++] = e;
             count[e] = 0;                // from here on: the next free slot of the expert's run
         }
+        tile_expert[max_tiles] = tile;
         for (; tile < max_tiles; ++tile) tile_expert[tile] = -1;
     }
     __syncthreads();

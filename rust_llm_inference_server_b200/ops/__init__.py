@@ -1151,7 +1151,7 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction, n_experts: in
     pairs = T * top
     tile = moe_tile_rows(pairs, n_experts)
     max_tiles = min(pairs, n_experts) + pairs // tile      # every expert in use ends in at most one partial tile
-    ints = step.buffer("moe_ints", (2 * pairs + max_tiles * tile + max_tiles,), torch.int32)
+    ints = step.buffer("moe_ints", (2 * pairs + max_tiles * tile + max_tiles + 1,), torch.int32)
     flts = step.buffer("moe_floats", (pairs + T,), torch.float32)
     top_idx, pair_slot = ints[:pairs], ints[pairs:2 * pairs]
     sorted_pair = ints[2 * pairs:2 * pairs + max_tiles * tile]
@@ -1178,7 +1178,8 @@ def _moe_grouped(plan: MoePlan, dtype, N: int, K: int) -> bool:
 def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor,
                          glu: tuple | None = None) -> torch.Tensor:
     """out[m] = x[m] @ w[e]^T for every row tile of 128 rows of x, e = tile_expert[tile] (-1: the tile is left
-    out and its rows of `out` keep what they held); on the tcgen05 tensor cores, one SM a tile.  x [M, K]
+    out and its rows of `out` keep what they held; such tiles come last, and tile_expert[M / 128] says how many
+    tiles have an expert); on the tcgen05 tensor cores, one SM a tile.  x [M, K]
     bfloat16 with M a multiple of 128; w [experts, N, K] bfloat16 contiguous; out [M, N] bfloat16 or float32.
     With `glu` = (slope, limit or None, up_shift): w's rows are gate and linear branch interleaved in blocks of
     4 and out [M, N / 2] bfloat16 is the gated result (see `glu_act`)."""
@@ -1188,8 +1189,8 @@ def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Te
     _req(w, "w", torch.bfloat16, (E, N, K))
     _req(tile_expert, "tile_expert", torch.int32, (None,))
     _req(out, "out", torch.bfloat16 if glu is not None else None, (M, N // 2 if glu is not None else N))
-    if M % 128 or tile_expert.shape[0] < M // 128 or out.dtype not in (torch.bfloat16, torch.float32):
-        raise KernelError(f"gemm_tcgen05_grouped: rows in tiles of 128 with an expert each, got M={M} and "
+    if M % 128 or tile_expert.shape[0] < M // 128 + 1 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"gemm_tcgen05_grouped: rows in tiles of 128 with an expert each and their count, got M={M} and "
                           f"{tile_expert.shape[0]} tiles; out in bfloat16 or float32, got {out.dtype}")
     slope, limit, shift = glu if glu is not None else (1.0, None, 0.0)
     code = 3 if glu is not None else 2 if out.dtype == torch.float32 else 0
