@@ -14,7 +14,9 @@ class RoutedFF(FeedForward):
     """Router scores in float32 from float32 copies of the router matrix (and of the shared expert's
     gate row, which rides along as one more row); choice, weights and the sort of (token, choice) pairs
     by expert happen on the device, so launches depend on the step's shape only.  The experts' matrices
-    are stacked [expert, out, in] at load time."""
+    are stacked at load time: both branches of the first product in one stack [expert, 2 I, in], the second
+    product's [expert, out, I].  Steps with many pairs an expert (portions of prompts) take the grouped
+    tcgen05 products, steps with few (decode) the mma.sync ones, float32 the FFMA ones (`ops.moe_up`)."""
 
     graph_safe = True
 
